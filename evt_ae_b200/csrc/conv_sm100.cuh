@@ -149,8 +149,7 @@ __device__ __forceinline__ void conv_kernel_body(const ConvParams& p) {
     mbar_fence_init();
   }
   if (warp == 1) {
-    if (lane == 0) hdr->tmem_base = 0xffffffffu;   // only the allocating warp touches this word
-    __syncwarp();
+    // the allocator writes the address asynchronously; no thread stores to that word
     tmem_alloc(&hdr->tmem_base, Cfg::TMEM_COLS);
     tmem_relinquish();
   }
@@ -158,8 +157,11 @@ __device__ __forceinline__ void conv_kernel_body(const ConvParams& p) {
   __syncthreads();
   tcgen05_fence_after_sync();
   const uint32_t tmem_base = hdr->tmem_base;
+  const bool tmem_ok = tmem_addr_valid(tmem_base, Cfg::TMEM_COLS);   // same value in every thread
 
-  if (warp == 0) {
+  if (!tmem_ok) {
+    if (threadIdx.x == 0) report_status(p.status, DEV_TMEM_ALLOC);
+  } else if (warp == 0) {
     // ------------------------------------------------------------------ TMA producer
     if (lane == 0) {
       tma_prefetch_desc(&p.tma_a);
@@ -300,7 +302,7 @@ __device__ __forceinline__ void conv_kernel_body(const ConvParams& p) {
   __syncthreads();
   if (warp == 1) {
     tcgen05_fence_after_sync();
-    if (tmem_base != 0xffffffffu) tmem_dealloc(tmem_base, Cfg::TMEM_COLS);
+    if (tmem_ok) tmem_dealloc(tmem_base, Cfg::TMEM_COLS);
   }
 }
 

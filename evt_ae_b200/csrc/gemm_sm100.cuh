@@ -140,7 +140,10 @@ struct GemmSmemHeader {
   uint64_t empty[8];
   uint64_t tmem_full[2];
   uint64_t tmem_empty[2];
-  uint32_t tmem_base;
+  // written by tcgen05.alloc only (asynchronously, not through the thread's own store path): no
+  // thread ever stores to this 16-byte slot, so nothing can land on top of the allocator's write
+  alignas(16) uint32_t tmem_base;
+  uint32_t tmem_base_pad[3];
   volatile int abort_flag;
   volatile int is_last;   // split-K: this CTA holds the last unit of its tile
   volatile int epi_abort; // split-K: an epilogue warp gave up; all leave after the same unit
@@ -290,10 +293,10 @@ __device__ __forceinline__ void gemm_kernel_body(const GemmParams& p) {
     mbar_fence_init();
   }
   if (warp == 1) {
-    // Only this warp touches tmem_base before the barrier: the allocator writes the
-    // address there asynchronously, so no other thread may store to the word meanwhile.
-    if (lane == 0) hdr->tmem_base = 0xffffffffu;
-    __syncwarp();
+    // The allocator writes the address asynchronously; no thread stores to that word, ever.  (A
+    // store issued just before the allocation by the same warp is not ordered with the
+    // allocator's write: when CTAs of other kernels shared the SM it landed afterwards and every
+    // tensor-memory access of the CTA then used the stale value.)
     tmem_alloc(&hdr->tmem_base, Cfg::TMEM_COLS);
     tmem_relinquish();
   }
@@ -301,8 +304,11 @@ __device__ __forceinline__ void gemm_kernel_body(const GemmParams& p) {
   __syncthreads();
   tcgen05_fence_after_sync();
   const uint32_t tmem_base = hdr->tmem_base;
+  const bool tmem_ok = tmem_addr_valid(tmem_base, Cfg::TMEM_COLS);   // same value in every thread
 
-  if (warp == 0) {
+  if (!tmem_ok) {
+    if (threadIdx.x == 0) report_status(p.status, DEV_TMEM_ALLOC);
+  } else if (warp == 0) {
     // ------------------------------------------------------------------ TMA producer
     if (lane == 0) {
       tma_prefetch_desc(&p.tma_a);
@@ -547,7 +553,7 @@ __device__ __forceinline__ void gemm_kernel_body(const GemmParams& p) {
   __syncthreads();
   if (warp == 1) {
     tcgen05_fence_after_sync();
-    if (tmem_base != 0xffffffffu) tmem_dealloc(tmem_base, Cfg::TMEM_COLS);
+    if (tmem_ok) tmem_dealloc(tmem_base, Cfg::TMEM_COLS);
   }
 }
 

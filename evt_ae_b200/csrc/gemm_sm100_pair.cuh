@@ -96,9 +96,7 @@ __device__ __forceinline__ void gemm_pair_kernel_body(const GemmParams& p) {
     mbar_fence_init();
   }
   if (warp == 1) {
-    // only this warp touches tmem_base before the barrier (the allocator writes it asynchronously)
-    if (lane == 0) hdr->tmem_base = 0xffffffffu;
-    __syncwarp();
+    // the allocator writes the address asynchronously; no thread stores to that word
     tmem_alloc_pair(&hdr->tmem_base, Cfg::TMEM_COLS);
     tmem_relinquish_pair();
   }
@@ -107,8 +105,13 @@ __device__ __forceinline__ void gemm_pair_kernel_body(const GemmParams& p) {
   cluster_sync_all();          // the peer's barriers are initialised before anything arrives on them
   tcgen05_fence_after_sync();
   const uint32_t tmem_base = hdr->tmem_base;
+  const bool tmem_ok = tmem_addr_valid(tmem_base, Cfg::TMEM_COLS);   // same value in every thread
 
-  if (warp == 0) {
+  if (!tmem_ok) {
+    // the peer's bounded waits run out and it meets this CTA at the cluster barrier below
+    if (threadIdx.x == 0) report_status(p.status, DEV_TMEM_ALLOC);
+    hdr->abort_flag = 1;
+  } else if (warp == 0) {
     // ------------------------------------------------------------------ TMA producer (both CTAs)
     if (lane == 0) {
       tma_prefetch_desc(&p.tma_a);
@@ -357,7 +360,7 @@ __device__ __forceinline__ void gemm_pair_kernel_body(const GemmParams& p) {
   cluster_sync_all();
   if (warp == 1) {
     tcgen05_fence_after_sync();
-    if (tmem_base != 0xffffffffu) tmem_dealloc_pair(tmem_base, Cfg::TMEM_COLS);
+    if (tmem_ok) tmem_dealloc_pair(tmem_base, Cfg::TMEM_COLS);
   }
 }
 

@@ -182,6 +182,11 @@ __device__ __forceinline__ void tmem_alloc(uint32_t* smem_result, uint32_t ncols
                : "memory");
 }
 
+// An allocation starts at lane 0 and leaves room for its columns inside the SM's 512.
+__device__ __forceinline__ bool tmem_addr_valid(uint32_t taddr, uint32_t ncols) {
+  return (taddr >> 16) == 0u && (taddr & 0xffffu) + ncols <= 512u;
+}
+
 __device__ __forceinline__ void tmem_relinquish() {
   asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
 }

@@ -5,7 +5,9 @@ benchmark configuration asks for data parallelism over 2/4/8 GPUs of one box wit
 all-reduce of the gradients over NVLink and nothing else partitioned.  One process per GPU;
 gradients are packed into a few large flat buckets (NVSwitch gives every peer full bandwidth,
 so bucket size is chosen for launch latency, not link count) and summed with
-`torch.distributed.all_reduce`, then averaged and unpacked in place.  Works on any backend:
+`torch.distributed.all_reduce`, then averaged and unpacked in place.  Every tensor starts on
+a 256-byte boundary of its bucket and bucket lengths are multiples of 256 bytes, so the pack /
+unpack kernels and the collective always take their vector paths.  Works on any backend:
 `nccl` on GPUs, `gloo` on CPU for the host-logic tests.
 """
 from __future__ import annotations
@@ -17,6 +19,8 @@ import torch.distributed as dist
 
 
 class GradAllReducer:
+    ALIGN_BYTES = 256
+
     def __init__(self, grads: Dict[str, torch.Tensor], bucket_bytes: int = 64 << 20, group=None, average: bool = True):
         """`grads`: name -> tensor (shapes / dtypes / device of what will be reduced every step;
         the same names in the same order on every rank)."""
@@ -33,18 +37,20 @@ class GradAllReducer:
             cur_elems = 0
             esize = torch.empty((), dtype=dt).element_size()
             limit = max(1, bucket_bytes // esize)
+            gran = max(1, self.ALIGN_BYTES // esize)       # elements per 256-byte granule
             for n in names:
                 k = grads[n].numel()
                 if cur and cur_elems + k > limit:
                     self._close(cur, cur_elems, dt, grads[names[0]].device)
                     cur, cur_elems = [], 0
                 cur.append((n, cur_elems, k))
-                cur_elems += k
+                cur_elems += (k + gran - 1) // gran * gran
             if cur:
                 self._close(cur, cur_elems, dt, grads[names[0]].device)
 
     def _close(self, entries, elems, dtype, device):
-        self.buckets.append((torch.empty(elems, dtype=dtype, device=device), list(entries)))
+        # zero-filled once: the padding between tensors takes part in the sum on every rank
+        self.buckets.append((torch.zeros(elems, dtype=dtype, device=device), list(entries)))
 
     @property
     def bytes_per_step(self) -> int:

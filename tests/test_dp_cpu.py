@@ -24,6 +24,10 @@ def _worker(rank, world, port, q):
     mine = {k: v.clone() for k, v in grads.items()}
     red = GradAllReducer(grads, bucket_bytes=4096)       # forces several buckets
     assert len(red.buckets) >= 3
+    for flat, entries in red.buckets:      # every tensor starts on a 256-byte boundary of its bucket
+        assert (flat.numel() * flat.element_size()) % 256 == 0
+        for _, off, _ in entries:
+            assert (off * flat.element_size()) % 256 == 0
     red.allreduce(grads)
     # expected: mean over ranks, rebuilt from the seeds
     ok = True
