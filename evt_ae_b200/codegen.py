@@ -930,7 +930,11 @@ class SpmmConfig:
     g: int            # lanes that share one nonzero's feature row (power of two, 8 columns each)
     vpt: int          # 8-column vectors per lane
     threads: int = 256
-    items_per_warp: int = 64
+    t_long: int = 128         # a lane group handles rows up to this many nonzeros alone
+    task_len: int = 1024      # nonzeros per task (one CTA) of the longer rows
+    u_short: int = 4          # nonzeros of a short row in flight per lane group
+    u_long: int = 4           # batches of 32 / g nonzeros in flight per warp in a task
+    min_ctas: int = 4         # resident CTAs per SM the register allocation is held to
 
     @property
     def f_pad(self) -> int:
@@ -946,7 +950,8 @@ def pick_spmm_config(F: int) -> SpmmConfig:
 
 
 def spmm_source(ir: EpilogueIR, dtype: torch.dtype, cfg: SpmmConfig, fused_norm: bool):
-    """Translation unit for one fused SpMM node: main kernel + fix-up kernel for split rows."""
+    """Translation unit for one fused SpMM node: main kernel + the launch that lists the tasks of
+    the long rows."""
     if ir.N % 8 != 0:
         raise NotImplementedError("SpMM needs a feature width that is a multiple of 8")
     epi = EpilogueGenerator(ir, row_tile=0, col_group=8).generate()
@@ -958,14 +963,14 @@ using namespace evtb;
 
 {epi.struct_code}
 
-extern "C" __global__ void __launch_bounds__({cfg.threads})
+extern "C" __global__ void __launch_bounds__({cfg.threads}, {cfg.min_ctas})
 evtb_spmm_kernel(const __grid_constant__ SpmmParams p) {{
-  spmm_body<{ct}, {cfg.g}, {cfg.vpt}, {norm}, Epi>(p);
+  spmm_body<{ct}, {cfg.g}, {cfg.vpt}, {norm}, {cfg.u_short}, {cfg.u_long}, {cfg.threads // 32}, Epi>(p);
 }}
 
-extern "C" __global__ void __launch_bounds__({cfg.threads})
-evtb_spmm_fixup_kernel(const __grid_constant__ SpmmParams p) {{
-  spmm_fixup_body<{cfg.g}, {cfg.vpt}, Epi>(p);
+extern "C" __global__ void __launch_bounds__(256)
+evtb_spmm_prep_kernel(const __grid_constant__ SpmmParams p) {{
+  spmm_prep_body(p);
 }}
 """
     return src, epi, "evtb_spmm_kernel"

@@ -317,8 +317,9 @@ struct evtb_plan {
   // convolution: everything of ConvParams that does not depend on the operand addresses
   evtb::ConvParams conv{};
   // SpMM
-  CUfunction fixup_fn = nullptr;
-  int total_warps = 0, items_per_warp = 0, fixup_grid = 0;
+  CUfunction prep_fn = nullptr;
+  int t_long = 0, task_len = 0, max_tasks = 0, long_ctas = 0, prep_grid = 0;
+  size_t spmm_tasks_off = 0, spmm_scratch_off = 0;
 };
 
 extern "C" {
@@ -523,26 +524,39 @@ int evtb_plan_create(const evtb_desc* desc, evtb_plan** out) {
     // operands [crow(int32), col(int32), val(fp32)|0, dinv(fp32)|0, X]; M = rows, N = F, K = nnz;
     // rows_per_cta = work items (rows + nonzeros) per warp; tile_n = padded feature width
     p->main_operands = 5;
-    if (d.K < 0 || d.rows_per_cta <= 0 || d.tile_n < d.N || d.M + d.K > 0x7fffff00LL) {
-      set_error("SpMM plan: bad nnz, items per warp or padded width");
+    if (d.K < 0 || d.rows_per_cta < 0 || d.stages < 0 || d.tile_n < d.N || d.tile_n % 8 != 0 ||
+        d.M + d.K > 0x7fffff00LL || d.threads % 32 != 0) {
+      set_error("SpMM plan: bad nnz, row-length threshold, task length or padded width");
       drv.ModuleUnload(p->module);
       delete p;
       return EVTB_EINVAL;
     }
-    r = drv.ModuleGetFunction(&p->fixup_fn, p->module, "evtb_spmm_fixup_kernel");
+    r = drv.ModuleGetFunction(&p->prep_fn, p->module, "evtb_spmm_prep_kernel");
     if (r != CUDA_SUCCESS) {
-      cu_fail("cuModuleGetFunction(evtb_spmm_fixup_kernel)", r);
+      cu_fail("cuModuleGetFunction(evtb_spmm_prep_kernel)", r);
       drv.ModuleUnload(p->module);
       delete p;
       return EVTB_ENOTFOUND;
     }
-    p->items_per_warp = d.rows_per_cta;
-    const long long items = d.M + d.K;
-    p->total_warps = static_cast<int>((items + p->items_per_warp - 1) / p->items_per_warp);
+    p->t_long = d.rows_per_cta > 0 ? d.rows_per_cta : 64;
+    p->task_len = d.stages > 0 ? d.stages : 1024;
+    // rows longer than t_long: fewer than nnz / t_long of them; every one adds at most one
+    // partly filled task to the nnz / task_len full ones
+    const long long max_tasks = d.K / (p->t_long + 1) + d.K / p->task_len + 2;
+    p->max_tasks = static_cast<int>(max_tasks);
+    auto up256 = [](size_t x) { return (x + 255) & ~static_cast<size_t>(255); };
+    p->spmm_tasks_off = up256(sizeof(unsigned int) * (1 + static_cast<size_t>(max_tasks)));
+    p->spmm_scratch_off = p->spmm_tasks_off + up256(sizeof(evtb::SpmmTask) * static_cast<size_t>(max_tasks));
+    p->workspace = p->spmm_scratch_off + sizeof(float) * static_cast<size_t>(max_tasks) * d.tile_n;
     const int wpc = d.threads / 32;
-    p->grid = (p->total_warps + wpc - 1) / wpc;
-    p->fixup_grid = p->grid;
-    p->workspace = sizeof(float) * static_cast<size_t>(p->total_warps) * d.tile_n;
+    const int g = d.tile_n / 8 < 32 ? d.tile_n / 8 : 32;            // lanes per row (power of two by construction)
+    const int rows_per_cta = wpc * (32 / (g > 0 ? g : 1));
+    const long long short_needed = (d.M + rows_per_cta - 1) / rows_per_cta;
+    const long long short_cap = 8ll * p->sm_count;
+    const int short_ctas = static_cast<int>(short_needed < short_cap ? short_needed : short_cap);
+    p->long_ctas = static_cast<int>(max_tasks < 2ll * p->sm_count ? max_tasks : 2ll * p->sm_count);
+    p->grid = p->long_ctas + (short_ctas > 0 ? short_ctas : 1);
+    p->prep_grid = static_cast<int>((d.M + 255) / 256);
   } else {
     // reduce-apply: persistent CTAs stride over row blocks
     //   SOFTMAX [x, rowmax_out|0, rowsum_out|0]   SOFTMAX_BWD [grad, y]   LAYERNORM [x, mean_out, invstd_out]
@@ -690,6 +704,10 @@ int evtb_launch_ex(evtb_plan* plan, const void* const* ptrs, int n, void* worksp
       set_error("SpMM plan needs a 16-byte aligned, once-zeroed workspace of evtb_plan_workspace_bytes() bytes");
       return EVTB_EINVAL;
     }
+    if (d.dtype == EVTB_F32 && (reinterpret_cast<uintptr_t>(ptrs[4]) & 31u) != 0) {
+      set_error("SpMM: fp32 features must be 32-byte aligned (they are gathered with 256-bit loads)");
+      return EVTB_EINVAL;
+    }
     evtb::SpmmParams sp;
     std::memset(&sp, 0, sizeof(sp));
     sp.crow = static_cast<const int*>(ptrs[0]);
@@ -701,19 +719,30 @@ int evtb_launch_ex(evtb_plan* plan, const void* const* ptrs, int n, void* worksp
       set_error("SpMM needs crow, col, X and exactly one of val / dinv");
       return EVTB_EINVAL;
     }
-    sp.scratch = static_cast<float*>(workspace);
+    char* ws = static_cast<char*>(workspace);
+    sp.counters = reinterpret_cast<unsigned int*>(ws);
+    sp.tasks = reinterpret_cast<evtb::SpmmTask*>(ws + plan->spmm_tasks_off);
+    sp.scratch = reinterpret_cast<float*>(ws + plan->spmm_scratch_off);
     sp.rows = static_cast<int>(d.M);
     sp.nnz = static_cast<int>(d.K);
     sp.F = static_cast<int>(d.N);
-    sp.total_warps = plan->total_warps;
-    sp.items_per_warp = plan->items_per_warp;
+    sp.t_long = plan->t_long;
+    sp.task_len = plan->task_len;
+    sp.long_ctas = plan->long_ctas;
+    sp.max_tasks = plan->max_tasks;
     sp.status = static_cast<int*>(status_word);
     sp.epi = epi;
     void* sargs[1] = {&sp};
-    CUresult sr = drv.LaunchKernel(plan->fn, plan->grid, 1, 1, d.threads, 1, 1, 0, static_cast<CUstream>(stream), sargs, nullptr);
+    // task count back to zero, task list of the long rows, then the main launch
+    if (cudaMemsetAsync(sp.counters, 0, sizeof(unsigned int), static_cast<cudaStream_t>(stream)) != cudaSuccess) {
+      set_error("cudaMemsetAsync(spmm task count) failed");
+      (void)cudaGetLastError();
+      return EVTB_ECUDA;
+    }
+    CUresult sr = drv.LaunchKernel(plan->prep_fn, plan->prep_grid, 1, 1, 256, 1, 1, 0, static_cast<CUstream>(stream), sargs, nullptr);
+    if (sr != CUDA_SUCCESS) return cu_fail("cuLaunchKernel(spmm preparation)", sr);
+    sr = drv.LaunchKernel(plan->fn, plan->grid, 1, 1, d.threads, 1, 1, 0, static_cast<CUstream>(stream), sargs, nullptr);
     if (sr != CUDA_SUCCESS) return cu_fail("cuLaunchKernel(spmm)", sr);
-    sr = drv.LaunchKernel(plan->fixup_fn, plan->fixup_grid, 1, 1, d.threads, 1, 1, 0, static_cast<CUstream>(stream), sargs, nullptr);
-    if (sr != CUDA_SUCCESS) return cu_fail("cuLaunchKernel(spmm fix-up)", sr);
     return EVTB_OK;
   }
 

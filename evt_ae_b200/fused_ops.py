@@ -610,7 +610,8 @@ class FusedSpmm(FusedOpBase):
         d.M, d.N, d.K, d.L = self.rows, self.F, self.nnz, 1
         d.threads = self.cfg.threads
         d.smem_bytes = 0
-        d.rows_per_cta = self.cfg.items_per_warp
+        d.rows_per_cta = self.cfg.t_long
+        d.stages = self.cfg.task_len
         d.tile_n = self.cfg.f_pad
         d.n_epilogue_ptrs = len(self.slots)
         d.image_path = self.image.encode()
@@ -634,6 +635,9 @@ class FusedSpmm(FusedOpBase):
         if col.shape[0] != self.nnz:
             raise RuntimeError(f"SpMM plan was built for {self.nnz} nonzeros, got {col.shape[0]}")
         wp = w.data_ptr()
+        if x.data_ptr() % 32 != 0:           # fp32 feature rows are gathered with 256-bit loads
+            x = x.clone()
+            keep.append(x)
         return [crow.data_ptr(), col.data_ptr(), 0 if self.fused_norm else wp, wp if self.fused_norm else 0, x.data_ptr()]
 
     @property

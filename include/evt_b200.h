@@ -50,7 +50,9 @@ enum evtb_kind {
   EVTB_LAYERNORM = 4,       /*                                               FusedLayerNorm         :829 */
   EVTB_LAYERNORM_BWD = 5,   /*                                               FusedLayerNormBackward :905 */
   EVTB_SPMM = 6,            /* CSR SpMM: operands [crow, col, val|0, dinv|0, X]; M = rows, N = F, K = nnz,
-                               rows_per_cta = work items per warp, tile_n = padded F   FusedSpmm   :973 */
+                               tile_n = padded F, rows_per_cta = longest row (in nonzeros) that a lane group
+                               handles alone (0: 64), stages = nonzeros per task of the longer rows (0: 1024).
+                               X must be 32-byte aligned for fp32 features.        FusedSpmm   :973 */
   EVTB_CONV_FPROP = 7,      /* NHWC implicit GEMM: operands [x (N,H,W,C), w (K,R,S,C)], result rows = N*P*Q,
                                columns = K; geometry in evtb_desc.conv         FusedConvFprop  evt_fuser.py:282 */
   EVTB_CONV_DGRAD = 8       /* data gradient: operands [dy (N,P,Q,K), w (K,R,S,C)], result rows = N*H*W,
@@ -128,7 +130,8 @@ const char* evtb_last_error(void);
 int evtb_plan_create(const evtb_desc* desc, evtb_plan** out);
 int evtb_plan_destroy(evtb_plan* plan);
 /* Scratch the caller must provide to evtb_launch (0 for most plans; split-K GEMMs keep their
- * fp32 partial tiles and per-tile arrival counters there).  It must be 16-byte aligned and
+ * fp32 partial tiles and per-tile arrival counters there, SpMM plans the task list and the
+ * partial sums of their long rows).  It must be 16-byte aligned and
  * ZERO-FILLED once before its first use; launches leave it ready for the next one.  Launches
  * that share a workspace must be ordered on one stream. */
 int evtb_plan_workspace_bytes(const evtb_plan* plan, size_t* bytes);
