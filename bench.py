@@ -130,9 +130,12 @@ class Config0Workload:
                 self.gm(*self.dev_inputs)
         torch.cuda.current_stream().wait_stream(side)
         torch.cuda.synchronize()
+        from evt_ae_b200 import runtime
+        before = runtime.KERNELS_ENQUEUED
         self.graph = torch.cuda.CUDAGraph()
         with torch.cuda.graph(self.graph, capture_error_mode="thread_local"):
             self.s_out = self.gm(*self.dev_inputs)
+        self.launches_per_step = runtime.KERNELS_ENQUEUED - before    # this library's kernels in one step
 
     def step_device(self):
         self.graph.replay()
@@ -229,7 +232,6 @@ class SpmmWorkload(Config0Workload):
         self.bytes = 4.0 * (n + 1) + 4.0 * nnz + 4.0 * n + 2 * 4.0 * n * F
         self.bytes_with_epilogue_inputs = self.fused.bytes_moved
         self.flops = 2.0 * self.fused.nnz * 128
-        self.launches_per_step = 2     # task list of the long rows + main kernel
 
     def value_from_ms(self, ms, n_gpus):
         return n_gpus * self.bytes / (ms * 1e-3) / 1e9
@@ -245,12 +247,16 @@ class BertLargeWorkload:
     metric = "BERT-large train-step samples/s per B200; fused GEMM TFLOP/s as % of tensor peak"
     unit = "samples/s"
     dtype = "bf16"
+    config_notes = ("timed step = embedding (eager), encoder + masked-LM head forward and backward on fused nodes, "
+                    "embedding backward; dropout is omitted (the reference's configuration sets p = 1e-19, "
+                    "mask == 1; fused dropout is tested on its own), the pooler and the next-sentence head "
+                    "(two M = 32 GEMMs) are outside the step, no optimizer update (the reference times zero_grad + "
+                    "forward + backward only, python/gtl/helper/test_helper.py:39-42)")
     cpu_sample = ("2 encoder layers + masked-LM head of the same model, batch 4 x sequence 512, fp32 eager "
                   "PyTorch forward + backward; samples/s scaled by (2-layer+head FLOPs)/(24-layer+head FLOPs)")
 
     def __init__(self, layers=24, B=32, S=512):
         from evt_ae_b200.workloads import bert as wb
-        layers = int(os.environ.get("EVT_B200_BERT_LAYERS", layers))   # debugging aid only
         self.wb = wb
         self.cfg = wb.BertConfig(layers=layers)
         self.B, self.S = B, S
@@ -285,6 +291,8 @@ class BertLargeWorkload:
         multi = dist.is_initialized() and dist.get_world_size() > 1
         self.graph = None
         self.segments = None        # data parallel: [(graph, gradients finished by it, their reducer)]
+        from evt_ae_b200 import runtime
+        launches_before = runtime.KERNELS_ENQUEUED
         if os.environ.get("MODE", "RUN") != "DEBUG":   # DEBUG synchronises per node: no capture
             if not multi:
                 self.graph = torch.cuda.CUDAGraph()
@@ -311,7 +319,9 @@ class BertLargeWorkload:
                     self.segments.append([g, part, None])
                     self.s_grads.update(part)
                 gen.close()
-        self.launches_per_step = self._count_launches()
+        # this library's kernels in one step, counted while the step was captured (torch's own small
+        # kernels around them -- embedding, loss bookkeeping, the arena memset -- are not included)
+        self.launches_per_step = (runtime.KERNELS_ENQUEUED - launches_before) or self._count_launches()
         self.host_loss = torch.zeros((), dtype=torch.float32).pin_memory()
         # data parallel: every rank is a replica; parameter gradients are all-reduced (NCCL)
         self.reducer = None
@@ -416,6 +426,34 @@ class BertLargeWorkload:
         args = [byname[n] for n in names]
         return "lin_hf_gelu (FFN1 GEMM 16384x4096x1024 + bias + GELU, 2 stores)", op.flops, op.time_kernel(args, iters=20, warmup=3)
 
+    def eager_gpu_ms(self, steps=5, warmup=2):
+        """The same model and batch as plain eager PyTorch bf16 autograd on this GPU (the oracle's
+        module moved to the device): the comparison the reference itself publishes (fused step
+        against PyTorch eager, benchmark/bert/bert.py:56-112).  A baseline, timed after the
+        main measurement; none of this library's kernels run in it."""
+        from oracle import bert_ref
+        cfg, dev, dt = self.cfg, self.device, torch.bfloat16
+        p = {k: v.to(dt).to(dev).requires_grad_(True) for k, v in bert_ref.init_params(cfg, seed=1235).items()}
+        ids, labels, mask = self.dev_in[0], self.dev_in[1], self.dev_in[2]
+
+        def step():
+            for v in p.values():
+                v.grad = None
+            x = bert_ref.embeddings(p, ids, cfg.eps)
+            loss = bert_ref.encoder_and_head_loss(p, cfg, x, mask, labels)
+            loss.backward()
+            return loss
+        for _ in range(warmup):
+            step()
+        torch.cuda.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(steps):
+            step()
+        e1.record()
+        torch.cuda.synchronize()
+        return e0.elapsed_time(e1) / steps
+
     # CPU side (oracle): a bounded slice of the same model
     def cpu_step(self):
         from oracle import bert_ref
@@ -465,6 +503,8 @@ def main():
     ap.add_argument("--impl", default="evt_b200", choices=["evt_b200", "reference"])
     ap.add_argument("--workload", default="bert", choices=sorted(WORKLOADS))
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--no-eager-baseline", action="store_true",
+                    help="skip the eager PyTorch bf16 step on the same GPU (an extra, labelled field)")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3) if args.impl == "evt_b200" else args.warmup
 
@@ -554,7 +594,9 @@ def main():
             achieved = kflops / (kernel_ms * 1e-3) / 1e12
             step_tflops = wl.flops / (ms * 1e-3) / 1e12
             roofline = dict(bound="tensor", achieved=achieved, peak=peak, unit="TFLOP/s", frac=achieved / peak,
-                            traffic=FFN1_DRAM_TRAFFIC_BYTES, traffic_unit="bytes per launch (dram read + write, ncu)",
+                            traffic=FFN1_DRAM_TRAFFIC_BYTES,
+                            traffic_unit="bytes per launch (dram read + write), from the ncu capture summarised in "
+                                         "profiles/bert_ffn1_gemm_ncu_metrics.md, not measured in this run",
                             algorithmic_bytes=FFN1_ALGORITHMIC_BYTES, kernel=kname, kernel_ms=kernel_ms,
                             peak_source=f"{peaks['source']} (burst: kernel timed alone)",
                             step_gemm_tflops=step_tflops, step_gemm_flops=wl.flops,
@@ -579,17 +621,29 @@ def main():
             cpu = dict(value=(wl.cpu_value(cpu_s) if hasattr(wl, "cpu_value") else wl.value_from_ms(cpu_s * 1e3, 1)),
                        unit=wl.unit, cores=cores, kind="port",
                        sample=wl.cpu_sample, seconds=cpu_s)
+        eager = None
+        if world == 1 and hasattr(wl, "eager_gpu_ms") and not args.no_eager_baseline:
+            try:
+                eager_ms = wl.eager_gpu_ms()
+                eager = dict(ms_per_step=eager_ms, value=wl.value_from_ms(eager_ms, 1), unit=wl.unit,
+                             speedup_of_fused_step=eager_ms / ms,
+                             what="the same model and batch, eager PyTorch bf16 autograd on this GPU (baseline)")
+            except Exception as e:   # the baseline must not take the measurement down
+                eager = dict(error=repr(e)[:200])
+        notes = getattr(wl, "config_notes", None)
         line = dict(metric=wl.metric, value=value, unit=wl.unit, n_gpus=world, steps=args.steps,
                     warmup=args.warmup, ms_per_step=ms, higher_is_better=True, scaling="weak",
                     vs_baseline=None, dtype=wl.dtype, data="synthetic",
                     config=dict(workload=wl.name, l2="working set per step far exceeds the 126 MB L2",
+                                **({"notes": notes} if notes else {}),
                                 parallelism=(f"dp{world}: one replica per GPU, per-GPU batch fixed, NCCL gradient all-reduce "
                                              f"({getattr(wl, 'bytes_reduced_per_step', 0) / 1e6:.0f} MB per step, overlapped with the backward pass in four segments)"
                                              if world > 1 else "single GPU")),
                     roofline=roofline, cpu_baseline=cpu,
                     e2e=dict(value=e2e_val, unit=wl.unit, ms_per_step=ms_e2e,
                              h2d_bytes_per_step=wl.h2d_bytes(), d2h_bytes_per_step=wl.d2h_bytes()),
-                    gpu_launches=wl.launches_per_step * args.steps, clocks=clocks)
+                    gpu_launches=wl.launches_per_step * args.steps, clocks=clocks,
+                    **({"eager_torch_gpu": eager} if eager is not None else {}))
         print(json.dumps(line))
     if dist is not None:
         dist.destroy_process_group()

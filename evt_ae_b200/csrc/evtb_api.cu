@@ -14,6 +14,7 @@
 #include <vector>
 
 #include "../../include/evt_b200.h"
+#include "evtb_internal.h"
 #include "conv_sm100.cuh"
 #include "gemm_sm100.cuh"
 #include "reduce_apply.cuh"
@@ -178,6 +179,8 @@ int encode_store_map(CUtensorMap* map, void* base, int64_t cols, int64_t rows, i
 
 int ceil_div(int a, int b) { return (a + b - 1) / b; }
 
+constexpr long long kIntMax = 0x7fffffffLL;
+
 // Fills plan->conv: parity classes, taps, the 128-position box and the tile counts.
 int plan_convolution(const evtb_desc& d, evtb::ConvParams& cp, int* grid, int sm_count) {
   const evtb_conv& g = d.conv;
@@ -297,6 +300,29 @@ int plan_convolution(const evtb_desc& d, evtb::ConvParams& cp, int* grid, int sm
 
 }  // namespace
 
+namespace evtb {
+
+void set_last_error(const std::string& text) { set_error(text); }
+
+int current_device_sm_count() {
+  static int cached[64] = {0};
+  int dev = -1;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0) {
+    (void)cudaGetLastError();
+    return 0;
+  }
+  if (dev < 64 && cached[dev] > 0) return cached[dev];
+  int n = 0;
+  if (cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess) {
+    (void)cudaGetLastError();
+    return 0;
+  }
+  if (dev < 64) cached[dev] = n;
+  return n;
+}
+
+}  // namespace evtb
+
 // ---------------------------------------------------------------------------
 // plan
 // ---------------------------------------------------------------------------
@@ -359,6 +385,24 @@ int evtb_plan_create(const evtb_desc* desc, evtb_plan** out) {
   if (d.n_epilogue_ptrs < 0 || d.n_epilogue_ptrs > evtb::kMaxEpiPtrs) {
     set_error("too many epilogue pointer slots");
     return EVTB_EINVAL;
+  }
+  // the kernels index with 32-bit integers: sizes, strides and the number of work units must fit
+  {
+    const long long k = d.K > 0 ? d.K : 1, l = d.L > 0 ? d.L : 1;
+    const long long strides[4] = {d.a.stride_outer, d.a.stride_batch, d.b.stride_outer, d.b.stride_batch};
+    bool fits = d.M <= kIntMax && d.N <= kIntMax && k <= kIntMax && l <= kIntMax;
+    if (d.kind == EVTB_GEMM || d.kind == EVTB_BGEMM)
+      for (long long s : strides) fits = fits && s >= 0;
+    if (fits && (d.kind == EVTB_GEMM || d.kind == EVTB_BGEMM) && d.tile_n > 0) {
+      const long long tm = (d.M + 127) / 128, tn = (d.N + d.tile_n - 1) / d.tile_n;
+      const long long splits = d.split_k > 1 ? d.split_k : 1;
+      // tm * tn * l * splits without overflowing 64 bits
+      fits = tm <= kIntMax / tn && tm * tn <= kIntMax / l && tm * tn * l <= kIntMax / splits;
+    }
+    if (!fits) {
+      set_error("plan: a size, a stride or the number of work units does not fit 32-bit indexing");
+      return EVTB_EINVAL;
+    }
   }
   if (d.kind == EVTB_GEMM || d.kind == EVTB_BGEMM) {
     if (d.K <= 0 || d.L <= 0 || (d.kind == EVTB_GEMM && d.L != 1)) {

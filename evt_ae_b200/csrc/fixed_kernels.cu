@@ -16,6 +16,7 @@
 #include <cub/device/device_select.cuh>
 
 #include "../../include/evt_b200.h"
+#include "evtb_internal.h"
 #include "epilogue_ops.cuh"
 #include "spmm.cuh"
 
@@ -146,13 +147,17 @@ struct ColsumPlan {
   size_t bytes;
 };
 
+// The chunk count depends only on the shape (a workspace size is asked for without a device):
+// sized for 148 SMs x 16 resident CTAs of 128 threads, which also fills smaller parts.
+constexpr int kColsumTargetCtas = 148 * 16;
+
 inline ColsumPlan colsum_plan(long long rows, long long cols, long long max_partial_floats = (1ll << 40)) {
   ColsumPlan p;
   p.col_blocks = static_cast<int>((cols + kColsumColsPerCta - 1) / kColsumColsPerCta);
   p.cols_padded = p.col_blocks * kColsumColsPerCta;
-  // enough CTAs to fill the GPU a few times over (16 resident CTAs of 128 threads per SM),
-  // at least 32 rows per chunk, within the scratch the caller has
-  long long want = (148 * 16 + p.col_blocks - 1) / p.col_blocks;
+  // enough CTAs to fill the GPU a few times over, at least 32 rows per chunk, within the scratch
+  // the caller has
+  long long want = (kColsumTargetCtas + p.col_blocks - 1) / p.col_blocks;
   long long max_by_rows = (rows + 31) / 32;
   long long chunks = want < max_by_rows ? want : max_by_rows;
   if (chunks > kColsumMaxChunks) chunks = kColsumMaxChunks;
@@ -279,13 +284,22 @@ static std::mutex g_scratch_mutex;
 // looked up once per device with that device current.
 static int static_scratch_address(void** out) {
   int dev = -1;
-  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= kMaxDevices) return EVTB_ECUDA;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0) {
+    (void)cudaGetLastError();
+    set_last_error("evtb_colsum_static: no current CUDA device");
+    return EVTB_ECUDA;
+  }
+  if (dev >= kMaxDevices) {
+    set_last_error("evtb_colsum_static: device ordinals above 63 are not supported");
+    return EVTB_EINVAL;
+  }
   std::lock_guard<std::mutex> lock(g_scratch_mutex);
   if (!g_scratch_ready[dev]) {
     void* p = nullptr;
     cudaError_t e = cudaGetSymbolAddress(&p, g_colsum_scratch);
     if (e != cudaSuccess || p == nullptr) {
       (void)cudaGetLastError();
+      set_last_error(std::string("evtb_colsum_static: cudaGetSymbolAddress failed: ") + cudaGetErrorString(e));
       return EVTB_ECUDA;
     }
     g_scratch_addr[dev] = p;
@@ -312,7 +326,9 @@ int evtb_colsum_accumulate(const void* x, int32_t in_dtype, int64_t rows, int64_
   const int r = static_cast<int>(rows), c = static_cast<int>(cols);
   const int col_blocks = (c + evtb::kColsumColsPerCta - 1) / evtb::kColsumColsPerCta;
   // about four CTAs per SM in total; every CTA adds its rows' sums to y with one atomic per column
-  int chunks = (148 * 4 + col_blocks - 1) / col_blocks;
+  int sms = evtb::current_device_sm_count();
+  if (sms <= 0) sms = 148;
+  int chunks = (sms * 4 + col_blocks - 1) / col_blocks;
   if (chunks > r) chunks = r;
   if (chunks < 1) chunks = 1;
   const int rows_per_chunk = (r + chunks - 1) / chunks;
@@ -416,7 +432,23 @@ int evtb_colsum_static(const void* x, int32_t in_dtype, int64_t rows, int64_t co
   if (pl.chunks < 1 || sizeof(float) * static_cast<size_t>(pl.chunks) * pl.cols_padded > evtb::kStaticPartialBytes ||
       sizeof(unsigned int) * pl.col_blocks > evtb::kStaticCounterBytes)
     return EVTB_ETOOLARGE;
-  if ((reinterpret_cast<uintptr_t>(x) & 15u) != 0) return EVTB_EINVAL;
+  // rows are read with 16-byte loads only when every row starts on a 16-byte boundary
+  if (cols % 8 == 0 && (reinterpret_cast<uintptr_t>(x) & 15u) != 0) {
+    evtb::set_last_error("evtb_colsum_static: x must be 16-byte aligned when cols is a multiple of 8");
+    return EVTB_EINVAL;
+  }
+  // the scratch array used is the CURRENT device's copy: the buffers (and the stream) must belong
+  // to that device, or the partial sums would be written through another GPU's memory
+  {
+    cudaPointerAttributes attr;
+    int dev = -1;
+    if (cudaGetDevice(&dev) == cudaSuccess && cudaPointerGetAttributes(&attr, x) == cudaSuccess &&
+        attr.type == cudaMemoryTypeDevice && attr.device != dev) {
+      evtb::set_last_error("evtb_colsum_static: x lives on another device than the current one");
+      return EVTB_EINVAL;
+    }
+    (void)cudaGetLastError();
+  }
   void* base = nullptr;
   const int rc = evtb::static_scratch_address(&base);   // first call on a device: symbol look-up
   if (rc != EVTB_OK) return rc;

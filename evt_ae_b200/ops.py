@@ -179,6 +179,7 @@ def colsum(x: torch.Tensor, out_dtype: torch.dtype = None) -> torch.Tensor:
             y = torch.zeros(cols, dtype=torch.float32, device=x.device)
         st = lib.evtb_colsum_accumulate(x.data_ptr(), _DT[x.dtype], rows, cols, y.data_ptr(), stream.cuda_stream)
         runtime._check(lib, st, "evtb_colsum_accumulate")
+        runtime.KERNELS_ENQUEUED += 1
         return y
     y = torch.empty(cols, dtype=out_dtype, device=x.device)
     nbytes = ctypes.c_size_t()
@@ -191,6 +192,7 @@ def colsum(x: torch.Tensor, out_dtype: torch.dtype = None) -> torch.Tensor:
     st = lib.evtb_colsum(x.data_ptr(), _DT[x.dtype], rows, cols, y.data_ptr(), _DT[out_dtype], ws.data_ptr(),
                          ws.numel() * 4, stream.cuda_stream)
     runtime._check(lib, st, "evtb_colsum")
+    runtime.KERNELS_ENQUEUED += 1
     return y
 
 
@@ -207,6 +209,7 @@ def sddmm(crow: torch.Tensor, col: torch.Tensor, u: torch.Tensor, v: torch.Tenso
     st = lib.evtb_sddmm(crow.data_ptr(), col.data_ptr(), u.data_ptr(), v.data_ptr(), rows, nnz, F, out.data_ptr(),
                         torch.cuda.current_stream().cuda_stream)
     runtime._check(lib, st, "evtb_sddmm")
+    runtime.KERNELS_ENQUEUED += 1
     return out
 
 

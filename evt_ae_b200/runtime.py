@@ -61,6 +61,10 @@ class evtb_scalars(ctypes.Structure):
 
 _lib = None
 
+# kernels of this library enqueued through this binding since import (a launch captured into a
+# CUDA graph counts once, at capture): lets a caller state how many of them one step holds
+KERNELS_ENQUEUED = 0
+
 
 def load_library() -> ctypes.CDLL:
     """Load libevt_b200.so from the package directory.  Raises if it was not built."""
@@ -129,6 +133,7 @@ class Plan:
         self.grid = g.value
         self.n_ptrs = self.num_main_operands + desc.n_epilogue_ptrs
         self._ptr_array = (ctypes.c_void_p * self.n_ptrs)()
+        self.kernels_per_launch = 2 if desc.kind == EVTB_SPMM else 1     # SpMM: task list + main kernel
 
     def launch(self, ptrs: Sequence[int], stream: int, status_ptr: int = 0, workspace_ptr: int = 0,
                scalars: Optional[evtb_scalars] = None):
@@ -143,6 +148,8 @@ class Plan:
             st = self.lib.evtb_launch_ex(self.handle, arr, self.n_ptrs, workspace_ptr, status_ptr, stream,
                                          ctypes.byref(scalars))
         _check(self.lib, st, "evtb_launch")
+        global KERNELS_ENQUEUED
+        KERNELS_ENQUEUED += self.kernels_per_launch
 
     def set_profile_buffer(self, device_ptr: int):
         """grid x 8 int64 counters written by kernels built with EVT_B200_KPROFILE=1."""

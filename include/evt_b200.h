@@ -193,8 +193,10 @@ int evtb_csr_build(const int32_t* coo_row, const int32_t* coo_col, int64_t n_edg
  *     EVTB_ETOOLARGE and launch nothing;
  *   - this function and everything it calls allocates nothing (no cudaMalloc / cudaFree, no
  *     torch allocation); inputs and outputs are still the caller's;
- *   - the first call on each device looks the array's device address up (a host-side CUDA
- *     query, made with that device current); make that first call outside any stream capture;
+ *   - every call uses the array of the CURRENT device: make the device that owns x, y and the
+ *     stream current before calling (a buffer of another device is refused with EVTB_EINVAL);
+ *     the first call on each device looks the array's device address up (a host-side CUDA
+ *     query); make that first call outside any stream capture;
  *   - all calls share the one array: calls whose kernels may overlap on the GPU (different
  *     streams, no ordering between them) race and give wrong sums.  Order them. */
 int evtb_colsum_static_max_cols(void);

@@ -42,9 +42,14 @@ def run_unfused_fp32(module: torch.nn.Module, inputs: Sequence[torch.Tensor]):
     return tuple(out)
 
 
-def compare(out: torch.Tensor, ref: torch.Tensor, kind: str = "half", scale_atol: float = 1.0) -> Dict[str, float]:
-    """Returns max abs / max rel error and the fraction of elements outside the tolerance.
-    Integer and boolean tensors must match exactly."""
+def compare(out: torch.Tensor, ref: torch.Tensor, kind: str = "half", scale_atol: float = 1.0,
+            reduction: bool = False) -> Dict[str, float]:
+    """Returns max abs / max rel error and the fraction of elements outside the tolerance
+    |out - ref| <= rtol |ref| + floor.  The absolute floor is tied to the magnitude of the
+    reference itself: atol x max(1, RMS(ref)) for an elementwise result (the resolution of 16-bit
+    storage at that magnitude), rtol x RMS(ref) for a reduction result (sums of terms of both
+    signs land near zero, where a relative bound per element means nothing).  Integer and boolean
+    tensors must match exactly."""
     out = out.detach().cpu()
     ref = ref.detach().cpu()
     assert out.shape == ref.shape, (out.shape, ref.shape)
@@ -55,7 +60,10 @@ def compare(out: torch.Tensor, ref: torch.Tensor, kind: str = "half", scale_atol
     r = ref.to(torch.float64)
     tol = TOL[kind]
     err = (o - r).abs()
-    bad = err > (tol["rtol"] * r.abs() + tol["atol"] * scale_atol)
+    finite = r[torch.isfinite(r)]
+    rms = float(finite.pow(2).mean().sqrt()) if finite.numel() else 0.0
+    floor = max(tol["atol"], tol["rtol"] * rms) if reduction else tol["atol"] * max(1.0, rms)
+    bad = err > (tol["rtol"] * r.abs() + floor * scale_atol)
     bad |= torch.isnan(o) != torch.isnan(r)
     rel = err / r.abs().clamp_min(1e-6)
     return dict(max_abs=err.max().item() if err.numel() else 0.0,

@@ -80,8 +80,39 @@ def _conv_dgrad_bn(g):
     return [grad_y, x, w, bn_input, mean, torch.ops.aten.rsqrt(var), gamma]
 
 
+def _pooler(g):
+    w = g.randn((1024, 1024)) * 0.018
+    x = g.randn((4, 1024))
+    b = g.randn((1024,)) * 0.018
+    return [x, w, b]
+
+
+def _nsp(g):
+    w, x, b = g.randn((2, 1024)), g.randn((2, 1024)), g.randn((2,))
+    return [x, w, b]
+
+
+def _softmax_col(g):
+    return [g.randn((16384, 512)), g.randn((16384, 1))]
+
+
 # name: (reference file, test method, inputs(g), case factory)
 CASES = {
+    "mm_partition2": ("mm.py", "test_mm_partition2", _pooler, lambda: P.mm_bias_tanh_only(4, 1024, 1024, f16)),
+    "mm_partition4": ("mm.py", "test_mm_partition4", _nsp, lambda: P.mm_bias_tiny_view(2, 2, 1024, f16)),
+    "mm_partition9": ("mm.py", "test_mm_partition9", _pooler, lambda: P.mm_bias_tanh(4, 1024, 1024, f16)),
+    "mm_partition12": ("mm.py", "test_mm_partition12", _plain((512, 24576), (1024, 24576), (512,)),
+                       lambda: P.mm_relu_dropout(1024, 512, 24576, 1e-19, f16)),
+    "softmax_aux_load": ("softmax.py", "test_softmax_aux_load", _plain((16384, 512), (16384, 512)),
+                         lambda: P.softmax_epilogue_form("aux", 16384, 512, f16)),
+    "softmax_row_broadcast": ("softmax.py", "test_softmax_row_broadcast", _plain((16384, 512), (512,)),
+                              lambda: P.softmax_epilogue_form("row", 16384, 512, f16)),
+    "softmax_scalar_broadcast": ("softmax.py", "test_softmax_scalar_broadcast", _plain((16384, 512)),
+                                 lambda: P.softmax_epilogue_form("scalar", 16384, 512, f16)),
+    "softmax_column_reduce": ("softmax.py", "test_softmax_column_reduce", _plain((16, 512)),
+                              lambda: P.softmax_epilogue_form("colreduce", 16, 512, f16)),
+    "softmax_column_broadcast": ("softmax.py", "test_softmax_column_broadcast", _softmax_col,
+                                 lambda: P.softmax_epilogue_form("col", 16384, 512, f16)),
     "mm_partition1": ("mm.py", "test_mm_partition1", _plain((4096, 1024), (1024, 1024), (4096,)),
                       lambda: P.mm_bias_gelu(1024, 4096, 1024, 512, 2, f16, "tanh")),
     "mm_partition3": ("mm.py", "test_mm_partition3", _plain((1024, 1024), (1024, 1024), (1024,)),
@@ -125,7 +156,19 @@ ORACLE_RTOL = {"conv_dgrad_partition1": 1e-4}
 # tests that create their inputs in another order than they pass them (draw k <-> creation order)
 INPUT_ORDER = {"softmaxbackward": [1, 0], "mm_partition3": [1, 0, 2]}
 
-SEED_BASE = {name: 100000 + 100 * i for i, name in enumerate(CASES)}
+# a module that draws its own random numbers (fused dropout): the reference's draw is the one
+# after the inputs; with keep probability 1 - 1e-19 the mask is all ones whatever the generator
+RANDOM_MASK_OUTPUTS = {"mm_partition12": [1]}
+
+# the first entries were added after the fixture's first version: seeds are tied to names
+_ORDER = ["mm_partition1", "mm_partition3", "mm_partition5", "mm_partition6", "mm_partition7", "mm_partition10",
+          "mm_partition11", "bmm_partition1", "bmm_partition2", "bmm_partition3", "softmax_aux_store",
+          "softmaxbackward", "layer_norm_pattern1", "layer_norm_pattern2", "layer_norm_backward_pattern1",
+          "conv_dgrad_partition1", "conv_dgrad_strided", "mm_partition2", "mm_partition4", "mm_partition9",
+          "mm_partition12", "softmax_aux_load", "softmax_row_broadcast", "softmax_scalar_broadcast",
+          "softmax_column_reduce", "softmax_column_broadcast"]
+assert sorted(_ORDER) == sorted(CASES)
+SEED_BASE = {name: 100000 + 100 * i for i, name in enumerate(_ORDER)}
 N_SAMPLES = 4096
 
 
@@ -141,3 +184,103 @@ def sample_index(numel: int) -> np.ndarray:
     if numel <= N_SAMPLES:
         return np.arange(numel)
     return (np.arange(N_SAMPLES, dtype=np.int64) * 2654435761 % numel).astype(np.int64)
+
+
+# ---------------------------------------------------------------------------------------------
+# Wrapped leaf functions of the reference's decomposition pass
+# (python/gtl/compiler/passes/pass_decomposition.py:61-189) against this package's leaves of the
+# same names (evt_ae_b200/ops.py).  `ref_args` builds the reference's arguments, `our_args` ours,
+# from the same seeded tensors; outputs are compared position by position.
+# ---------------------------------------------------------------------------------------------
+LEAF_SEED = 200000
+CONV = dict(N=8, H=28, W=28, C=64, K=128, R=3, stride=[1, 1], padding=[1, 1], dilation=[1, 1])
+CONV_S2 = dict(N=8, H=28, W=28, C=64, K=128, R=3, stride=[2, 2], padding=[1, 1], dilation=[1, 1])
+SPMM = dict(n=3001, edges=20000, F=64)
+
+
+def _conv_tensors(geo, base):
+    n, h, w, c, k, r = (geo[x] for x in "NHWCKR")
+    p = (h + 2 * geo["padding"][0] - r) // geo["stride"][0] + 1
+    x = P.seeded((n, h, w, c), base, 1.0, f16)
+    wt = P.seeded((k, r, r, c), base + 1, 0.05, f16)
+    dy = P.seeded((n, p, p, k), base + 2, 1.0, f16)
+    return x, wt, dy
+
+
+def _bn_tensors(base):
+    x = P.seeded((8, 14, 14, 64), base, 2.0, f16) + 1.0
+    dy = P.seeded((8, 14, 14, 64), base + 1, 1.0, f16)
+    gamma, beta = P.seeded((64,), base + 2, 1.0, f16), P.seeded((64,), base + 3, 1.0, f16)
+    return x, dy, gamma, beta
+
+
+def leaf_inputs(name):
+    """dict of seeded tensors (and the call's plain arguments) for one leaf."""
+    if name == "spmm":
+        case = P.spmm_case(SPMM["n"], SPMM["edges"], SPMM["F"], "plain")
+        crow, col, val, x = case.inputs
+        return dict(crow=crow, col=col, val=val, x=x)
+    if name in ("conv_fprop", "conv_dgrad"):
+        x, w, dy = _conv_tensors(CONV, LEAF_SEED + 10)
+        return dict(x=x, w=w, dy=dy, geo=CONV)
+    if name in ("conv_fprop_s2", "conv_dgrad_s2"):
+        x, w, dy = _conv_tensors(CONV_S2, LEAF_SEED + 20)
+        return dict(x=x, w=w, dy=dy, geo=CONV_S2)
+    x, dy, gamma, beta = _bn_tensors(LEAF_SEED + 30)
+    return dict(x=x, dy=dy, gamma=gamma, beta=beta, eps=1e-5, rf=1.0 / (8 * 14 * 14))
+
+
+def _f32(t):
+    return t.to(torch.float32) if t.dtype in (torch.float16, torch.bfloat16) else t
+
+
+def leaf_call(fns, name, t, upcast=True):
+    """Calls leaf `name` of the namespace `fns` (the reference's module or evt_ae_b200.ops) on the
+    tensors `t`; returns a tuple of outputs.  `fns.spmm` of the reference takes a sparse CSR
+    tensor, this package's takes the three CSR arrays."""
+    u = _f32 if upcast else (lambda z: z)
+    if name == "spmm":
+        if getattr(fns, "__name__", "").endswith("ops"):
+            return (fns.spmm(t["crow"], t["col"], t["val"], t["x"]),)
+        a = torch.sparse_csr_tensor(t["crow"].to(torch.int64), t["col"].to(torch.int64), t["val"],
+                                    size=(t["crow"].shape[0] - 1, t["x"].shape[0]))
+        return (fns.spmm(a, t["x"]),)
+    if name.startswith("conv_fprop"):
+        g = t["geo"]
+        return (fns.convolution_forward_channel_last(u(t["x"]), u(t["w"]), g["stride"], g["padding"], g["dilation"],
+                                                     False, [0, 0], 1),)
+    if name.startswith("conv_dgrad"):
+        g = t["geo"]
+        return (fns.convolution_backward_data_channel_last(u(t["dy"]), u(t["x"]), u(t["w"]), g["stride"], g["padding"],
+                                                           g["dilation"], False, [0, 0], 1),)
+    # batch norm: the four leaves chained as the decomposed graph chains them
+    x, dy, gamma, beta = t["x"], t["dy"], t["gamma"], t["beta"]
+    mean, mean_x2 = fns.batch_norm_stat(x, t["rf"])
+    y, saved_mean, saved_rstd = fns.batch_norm_elemt(x, gamma, beta, mean, mean_x2, t["eps"], 64)
+    sum_dy, sum_dy_xhat = fns.batch_norm_backward_stat(dy, x, saved_mean, saved_rstd, 64)
+    dx, dgamma, dbeta = fns.batch_norm_backward_elemt(dy, x, saved_mean, saved_rstd, 64, sum_dy, sum_dy_xhat, t["rf"], gamma)
+    return (mean, mean_x2, y, saved_mean, saved_rstd, sum_dy, sum_dy_xhat, dx, dgamma, dbeta)
+
+
+LEAVES = ["spmm", "conv_fprop", "conv_dgrad", "conv_fprop_s2", "conv_dgrad_s2", "batch_norm"]
+
+# ---------------------------------------------------------------------------------------------
+# Dropout (unittest/evt_fuser/dropout.py:33-75): the reference module calls aten.native_dropout,
+# whose mask no other generator reproduces; the fixture keeps the mask the reference drew (packed
+# bits) and the result, and the restated module's formula is checked with that mask.
+# ---------------------------------------------------------------------------------------------
+DROPOUT_SEED = 300000
+DROPOUT_P = 0.7
+
+
+def dropout_inputs():
+    g = Draws(DROPOUT_SEED)
+    x, w, b, r = g.randn((1024, 1024)), g.randn((1024, 1024)), g.randn((1024,)), g.randn((512, 2, 1024))
+    return [x, w, b, r]
+
+
+def dropout_formula(inputs, keep):
+    """out of the restated module (cases.mm_bias_dropout_residual) for a given keep mask, fp32."""
+    x, w, b, r = [_f32(t) for t in inputs]
+    v = (x @ w.t() + b).view(512, 2, 1024)
+    return v * keep.to(torch.float32) * (1.0 / (1.0 - DROPOUT_P)) + r

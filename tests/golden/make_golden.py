@@ -78,23 +78,75 @@ def run_reference_test(ref_root: str, fname: str, method: str, draws: cases.Draw
     return fake.inputs, fake.outputs
 
 
+def load_reference_leaves(ref_root: str):
+    """Imports the reference's python/gtl/compiler/passes/pass_decomposition.py as it lies in the
+    checkout, without running the package __init__ files above it (they import the fuser, which
+    needs a CUTLASS fork that is not installable here): empty stand-in packages with the real
+    directories as their __path__ let the normal import machinery find the submodules."""
+    import importlib
+    base = os.path.join(ref_root, "python", "gtl")
+    for name, path in (("gtl", base), ("gtl.compiler", os.path.join(base, "compiler")),
+                       ("gtl.compiler.passes", os.path.join(base, "compiler", "passes"))):
+        if name not in sys.modules:
+            m = types.ModuleType(name)
+            m.__path__ = [path]
+            sys.modules[name] = m
+    return importlib.import_module("gtl.compiler.passes.pass_decomposition")
+
+
+def _store_outputs(store, key, outs):
+    store[f"{key}/n_out"] = np.array(len(outs))
+    for j, o in enumerate(outs):
+        flat = o.detach().to(torch.float64).reshape(-1).numpy() if o.dtype != torch.bool else o.reshape(-1).numpy().astype(np.float64)
+        idx = cases.sample_index(flat.size)
+        store[f"{key}/{j}/shape"] = np.array(o.shape, dtype=np.int64)
+        store[f"{key}/{j}/sample"] = flat[idx].astype(np.float32)
+        store[f"{key}/{j}/sum"] = np.array(flat.sum())
+        store[f"{key}/{j}/abs_sum"] = np.array(np.abs(flat).sum())
+
+
+def reference_dropout_module(ref_root: str):
+    """class Dropout1 as written inside unittest/evt_fuser/dropout.py:test_dropout."""
+    import operator
+    path = os.path.join(ref_root, "unittest", "evt_fuser", "dropout.py")
+    src = open(path).read()
+    for node in ast.walk(ast.parse(src)):
+        if isinstance(node, ast.ClassDef) and node.name == "Dropout1":
+            ns = {"torch": torch, "operator": operator}
+            exec(compile(textwrap.dedent(ast.get_source_segment(src, node)), path, "exec"), ns)
+            return ns["Dropout1"]()
+    raise KeyError("Dropout1 not found")
+
+
 def main():
     ref_root = sys.argv[1] if len(sys.argv) > 1 else os.environ.get("EVT_REFERENCE_ROOT", "reference")
     store = {}
+    # wrapped leaf functions of the reference's decomposition pass
+    ref_leaves = load_reference_leaves(ref_root)
+    for leaf in cases.LEAVES:
+        with torch.no_grad():
+            outs = cases.leaf_call(ref_leaves, leaf, cases.leaf_inputs(leaf))
+        _store_outputs(store, f"leaf/{leaf}", list(outs))
+        print("leaf", leaf, "ok:", [tuple(o.shape) for o in outs])
+    # dropout: the reference module with the mask it drew
+    mod = reference_dropout_module(ref_root)
+    ins = cases.dropout_inputs()
+    torch.manual_seed(cases.DROPOUT_SEED)
+    with torch.no_grad():
+        out, keep = mod(*[x.to(torch.float32) for x in ins])
+    assert keep.dtype == torch.bool and abs(keep.float().mean().item() - (1 - cases.DROPOUT_P)) < 1e-2
+    store["dropout/keep_bits"] = np.packbits(keep.reshape(-1).numpy())
+    _store_outputs(store, "dropout", [out])
+    print("dropout ok:", tuple(out.shape), "kept", keep.float().mean().item())
     for name, (fname, method, _, make_case) in cases.CASES.items():
         ref_in, ref_out = run_reference_test(ref_root, fname, method, cases.Draws(cases.SEED_BASE[name]))
         mine = cases.golden_inputs(name)
         assert len(mine) == len(ref_in), (name, len(mine), len(ref_in))
         for i, (a, b) in enumerate(zip(mine, ref_in)):
             assert a.dtype == b.dtype and a.shape == b.shape and torch.equal(a, b), f"{name}: input {i} differs"
-        store[f"{name}/n_out"] = np.array(len(ref_out))
-        for j, o in enumerate(ref_out):
-            flat = o.detach().to(torch.float64).reshape(-1).numpy() if o.dtype != torch.bool else o.reshape(-1).numpy().astype(np.float64)
-            idx = cases.sample_index(flat.size)
-            store[f"{name}/{j}/shape"] = np.array(o.shape, dtype=np.int64)
-            store[f"{name}/{j}/sample"] = flat[idx].astype(np.float32)
-            store[f"{name}/{j}/sum"] = np.array(flat.sum())
-            store[f"{name}/{j}/abs_sum"] = np.array(np.abs(flat).sum())
+        _store_outputs(store, name, ref_out)
+        for j in cases.RANDOM_MASK_OUTPUTS.get(name, []):
+            assert bool(ref_out[j].all()), f"{name}: the generated keep mask is not all ones"
         print(name, "ok:", [tuple(o.shape) for o in ref_out])
     np.savez_compressed(os.path.join(HERE, "golden.npz"), **store)
     print("wrote", os.path.join(HERE, "golden.npz"))

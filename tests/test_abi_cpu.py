@@ -83,3 +83,26 @@ def test_reduction_arena_hands_out_disjoint_zeroed_views():
         from evt_ae_b200 import fused_ops
         assert fused_ops._ACTIVE_ARENA is arena
     assert fused_ops._ACTIVE_ARENA is None
+
+
+def test_integration_note_shows_the_current_descriptor():
+    """The ctypes mirror of evtb_desc printed in INTEGRATION.md is what a maintainer copies: it
+    must list the fields of the binding this package uses, in order, and the header must declare
+    them in the same order."""
+    from evt_ae_b200 import runtime
+    text = open(os.path.join(ROOT, "INTEGRATION.md")).read()
+    block = text[text.index("class evtb_desc(ctypes.Structure):"):]
+    block = block[: block.index("\n\n")]
+    doc_fields = re.findall(r'\("(\w+)",', block)
+    mine = [f[0] for f in runtime.evtb_desc._fields_]
+    assert doc_fields == mine, (doc_fields, mine)
+    header = open(os.path.join(ROOT, "include", "evt_b200.h")).read()
+    body = header[header.index("typedef struct evtb_desc {") + len("typedef struct evtb_desc {"): header.index("} evtb_desc;")]
+    body = re.sub(r"/\*.*?\*/", "", body, flags=re.S)
+    header_fields = []
+    for decl in body.split(";"):
+        decl = decl.strip()
+        if decl:
+            names = decl.split(None, 1)[1] if not decl.startswith("const") else decl.split(None, 2)[2]
+            header_fields += [re.sub(r"[\*\s]|\[\d+\]", "", n) for n in names.split(",")]
+    assert header_fields == mine, (header_fields, mine)

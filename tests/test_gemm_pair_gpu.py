@@ -48,7 +48,7 @@ def test_pair_weight_gradient_long_k_twice(cuda_device):
         out = gm(*inputs)
         torch.cuda.synchronize()
         fused.check_status()
-        st = compare(out, ref, "half", scale_atol=30.0)
+        st = compare(out, ref, "half")
         assert st["bad_frac"] == 0.0, st
 
 

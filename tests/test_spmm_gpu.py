@@ -1,7 +1,7 @@
 """CSR SpMM (merge-path, generated epilogue), SDDMM and the CSR builder on the GPU through
-the C-ABI.  fp32 results: |out - ref| <= 1e-5 |ref| + 1e-5 * (row magnitude) -- hub rows add
-thousands of terms in a different order than the CPU; fp16 features: 1e-2 / 1e-3; CSR arrays
-bit-exact."""
+the C-ABI.  fp32 results: |out - ref| <= 1e-5 |ref| + 1e-5 x RMS of the row -- hub rows add
+thousands of terms of both signs in a different order than the CPU; fp16 features: 1e-2 / 1e-3;
+CSR arrays bit-exact."""
 import pytest
 import torch
 
@@ -15,7 +15,7 @@ pytestmark = pytest.mark.gpu
 
 def _check(out, ref, half):
     out, ref = out.detach().cpu().double(), ref.detach().cpu().double()
-    rowmag = ref.abs().amax(dim=-1, keepdim=True).clamp_min(1.0)
+    rowmag = ref.pow(2).mean(dim=-1, keepdim=True).sqrt()
     tol = (1e-2 * ref.abs() + 1e-3 * rowmag) if half else (1e-5 * ref.abs() + 1e-5 * rowmag)
     bad = (out - ref).abs() > tol
     assert not bad.any(), ((out - ref).abs().max().item(), int(bad.sum()))
