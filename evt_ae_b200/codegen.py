@@ -704,6 +704,7 @@ class GemmTileConfig:
     k_rotate: bool = False    # every CTA starts its K loop at a different k-block
     cta_pair: bool = False    # two CTAs of a cluster share a 256 x bn tile (tcgen05 cta_group::2)
     tma_store: bool = True    # results with a linear address leave through TMA bulk stores
+    staged: bool = True       # full tensors of the epilogue pass through shared-memory staging tiles
     row_resident: bool = False  # 128 x 512 tile = whole rows: a row-wise step runs in the epilogue (set by gemm_source)
 
     @property
@@ -717,7 +718,7 @@ def gemm_source(ir: EpilogueIR, a_major: str, b_major: str, dtype: torch.dtype,
     description, entry-point name)."""
     # a CTA pair covers 256 rows per tile: rows 128..255 of the last tile are out of range unless
     # M is a multiple of 256
-    epi = EpilogueGenerator(ir, row_tile=256 if cfg.cta_pair else 128, staged=True, tma_store=cfg.tma_store).generate()
+    epi = EpilogueGenerator(ir, row_tile=256 if cfg.cta_pair else 128, staged=cfg.staged, tma_store=cfg.tma_store and cfg.staged).generate()
     cfg.stage_tiles = epi.stage_tiles
     # the staging tiles come out of the shared memory the operand ring would otherwise get
     while cfg.stages > 2 and gemm_smem_bytes(cfg) > 227 * 1024:

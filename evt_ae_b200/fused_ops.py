@@ -450,7 +450,8 @@ class _FusedRowBase(FusedOpBase):
         self.dtype = _dtype(self.args[0])
         if self.dtype not in (torch.float16, torch.bfloat16, torch.float32):
             raise NotImplementedError(f"row kernel on {self.dtype}")
-        self.cfg = row_config or codegen.pick_row_config(self.cols, self.max_vpt)
+        self.tune_key = tuning.key_for_node("row", ir, (self.rows, self.cols), self.dtype)
+        self.cfg = row_config or self._tuned_row_config() or codegen.pick_row_config(self.cols, self.max_vpt)
         self.eps = trace.attrs.get("eps", 1e-12)
         gamma_dtype = None
         if self.kind == "layernorm_backward" and len(self.args) > 4 and self.args[4] is not None:
@@ -473,6 +474,12 @@ class _FusedRowBase(FusedOpBase):
         self.desc = d
         self.plan = runtime.Plan(d) if torch.cuda.is_available() else None
         self._aux = {}
+
+    def _tuned_row_config(self):
+        e = tuning.lookup_config(self.tune_key)
+        if e is None:
+            return None
+        return codegen.RowKernelConfig(tpr=int(e["tpr"]), vpt=int(e["vpt"]), threads=int(e["threads"]), vec=self.cols % 8 == 0)
 
     def _main_ptrs(self, main_tensors, keep):
         if self.plan is None:
@@ -598,7 +605,12 @@ class FusedSpmm(FusedOpBase):
         self.fused_norm = bool(trace.attrs.get("fused_norm", False))
         if _dtype(crow) != torch.int32 or _dtype(col) != torch.int32:
             raise NotImplementedError("SpMM needs int32 CSR indices")
+        self.tune_key = tuning.key_for_node("spmm", ir, (self.rows, self.F, self.nnz), self.dtype)
         self.cfg = spmm_config or codegen.pick_spmm_config(self.F)
+        e = None if spmm_config else tuning.lookup_config(self.tune_key)
+        if e is not None:
+            for f in ("t_long", "task_len", "u_short", "u_long", "min_ctas"):
+                setattr(self.cfg, f, int(e[f]))
         src, epi, entry = codegen.spmm_source(ir, self.dtype, self.cfg, self.fused_norm)
         self.source = src
         self.slots = epi.slots
@@ -681,7 +693,16 @@ class _FusedConvBase(FusedOpBase):
             raise NotImplementedError("fused convolutions need channel counts that are multiples of 64 "
                                       "(the 3-channel stem goes through a patch matrix and the GEMM)")
         import copy
-        self.tile = copy.copy(conv_tile) if conv_tile else codegen.ConvTileConfig(bn=256 if nt >= 256 else 128 if nt >= 128 else 64)
+        g = self.geom
+        self.tune_key = tuning.key_for_node("conv_dgrad" if self.dgrad else "conv_fprop", self.ir,
+                                            [g[k] for k in ("N", "H", "W", "C", "K", "R", "S", "stride_h", "pad_h")], self.dtype)
+        e = None if conv_tile else tuning.lookup_config(self.tune_key)
+        if conv_tile:
+            self.tile = copy.copy(conv_tile)
+        elif e is not None:
+            self.tile = codegen.ConvTileConfig(bn=int(e["bn"]), stages=int(e["stages"]), epi_warps=int(e["epi_warps"]))
+        else:
+            self.tile = codegen.ConvTileConfig(bn=256 if nt >= 256 else 128 if nt >= 128 else 64)
         src, epi, entry = codegen.conv_source(self.ir, self.dgrad, self.dtype, self.tile)
         self.source = src
         self.slots = epi.slots

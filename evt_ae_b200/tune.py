@@ -47,6 +47,8 @@ def candidates(op: _FusedMatmulBase) -> List[GemmTileConfig]:
             add(base.bn, ew, base.split_k, pair)
     if base.bn == 256:
         add(128, 8, base.split_k)
+        add(128, 8, base.split_k, True)      # 256 x 128 pair tiles: twice the tiles, fuller last wave
+        add(128, 16, base.split_k, True)
     tiles = ((op.M + 127) // 128) * ((op.N + base.bn - 1) // base.bn) * op.L
     num_k = (op.K + 63) // 64
     if tiles < 148 and num_k >= 32:
@@ -56,6 +58,67 @@ def candidates(op: _FusedMatmulBase) -> List[GemmTileConfig]:
                     add(bn, 8, sk)
                 add(256, 8, sk, True)
     return out
+
+
+def row_candidates(op) -> List:
+    """threads per row x CTA size around the closed-form choice (the row must fit the registers:
+    at most 8 vectors of 8 elements per thread)."""
+    from .codegen import RowKernelConfig
+    base = op.cfg
+    vectors = (op.cols + 7) // 8
+    out = [base]
+    for tpr in (base.tpr // 2, base.tpr, base.tpr * 2):
+        if tpr < 8 or tpr > 1024:
+            continue
+        vpt = (vectors + tpr - 1) // tpr
+        if vpt > 2 * op.max_vpt or vpt < 1:
+            continue
+        for threads in (128, 256, 512):
+            threads = max(threads, tpr)
+            c = RowKernelConfig(tpr=tpr, vpt=vpt, threads=threads, vec=base.vec)
+            if all((c.tpr, c.threads) != (o.tpr, o.threads) for o in out):
+                out.append(c)
+    return out
+
+
+def conv_candidates(op) -> List:
+    from .codegen import ConvTileConfig
+    nt = op.geom["C"] if op.dgrad else op.geom["K"]
+    out = [op.tile]
+    for bn in (64, 128, 256):
+        if bn > nt:
+            continue
+        for stages, ew in ((6, 8), (4, 8), (6, 16)):
+            c = ConvTileConfig(bn=bn, stages=stages, epi_warps=ew)
+            if all((c.bn, c.stages, c.epi_warps) != (o.bn, o.stages, o.epi_warps) for o in out):
+                out.append(c)
+    return out
+
+
+def spmm_candidates(op) -> List:
+    import copy
+    out = [op.cfg]
+    for t_long, task_len, u_short, min_ctas in [(64, 1024, 4, 4), (128, 1024, 4, 4), (256, 1024, 4, 4), (128, 512, 4, 4),
+                                               (128, 1024, 2, 4), (128, 1024, 4, 3)]:
+        c = copy.copy(op.cfg)
+        c.t_long, c.task_len, c.u_short, c.min_ctas = t_long, task_len, u_short, min_ctas
+        if all((c.t_long, c.task_len, c.u_short, c.min_ctas) != (o.t_long, o.task_len, o.u_short, o.min_ctas) for o in out):
+            out.append(c)
+    return out
+
+
+def node_candidates(op):
+    """(keyword of fuse_module, candidate list, fields stored in the table) for any fused node."""
+    from . import fused_ops as F
+    if isinstance(op, _FusedMatmulBase):
+        return "tile", candidates(op), ("bn", "stages", "epi_warps", "split_k", "cta_pair")
+    if isinstance(op, F._FusedRowBase):
+        return "row_config", row_candidates(op), ("tpr", "vpt", "threads")
+    if isinstance(op, F._FusedConvBase):
+        return "conv_tile", conv_candidates(op), ("bn", "stages", "epi_warps")
+    if isinstance(op, F.FusedSpmm):
+        return "spmm_config", spmm_candidates(op), ("t_long", "task_len", "u_short", "u_long", "min_ctas")
+    raise TypeError(type(op))
 
 
 def random_like(meta: torch.Tensor, device) -> torch.Tensor:
@@ -80,7 +143,21 @@ def workload_specs(name: str) -> Dict[str, Tuple[torch.nn.Module, list]]:
         step = wb.BertStep(wb.BERT_LARGE, 32, 512, dtype=torch.bfloat16)
         # row-resident nodes (softmax fused into the GEMM) have one configuration and are not tuned
         return {k: v for k, v in step.n.specs.items()
-                if isinstance(step.n.ops[k], _FusedMatmulBase) and not step.n.ops[k].tile.row_resident}
+                if not (isinstance(step.n.ops[k], _FusedMatmulBase) and step.n.ops[k].tile.row_resident)}
+    if name == "resnet_convs":
+        # forward convolutions with batch-norm statistics and strided data gradients at ResNet-50 shapes, batch 128
+        from .workloads import cases as P
+        out = {}
+        for (h, c, k, r, s) in [(56, 64, 64, 3, 1), (56, 64, 256, 1, 1), (28, 128, 128, 3, 1), (14, 256, 256, 3, 1), (7, 512, 512, 3, 1)]:
+            case = P.conv_fprop_bn_stat(128, h, h, c, k, r, s)
+            out[f"fprop_{h}_{c}_{k}_{r}"] = (case.module, [torch.empty(t.shape, dtype=t.dtype, device="meta") for t in case.inputs])
+        case = P.conv_dgrad_strided(128, 28, 28, 128, 256, 3, 2)
+        out["dgrad_28_128_256_s2"] = (case.module, [torch.empty(t.shape, dtype=t.dtype, device="meta") for t in case.inputs])
+        return out
+    if name == "gcn":
+        from .workloads import cases as P
+        case = P.spmm_case(169343, 585000, 128, "sym")
+        return {"agg_sym_128": (case.module, list(case.inputs))}
     if name == "config0":
         aten = torch.ops.aten
 
@@ -104,12 +181,15 @@ def main(argv=None):
                     help="a candidate replaces the closed-form choice only below this fraction of its time")
     a = ap.parse_args(argv)
     specs = workload_specs(a.workload)
+    def as_meta(ts):
+        return [torch.empty(t.shape, dtype=t.dtype, device="meta") if t.device.type != "meta" else t for t in ts]
     if a.compile_only:
         with jit.deferred() as d:
             for name, (module, metas) in specs.items():
-                _, op0 = fuse_module(module, metas)
-                for c in candidates(op0):
-                    fuse_module(module, metas, tile=c)
+                _, op0 = fuse_module(module, as_meta(metas))
+                kw, cands, _ = node_candidates(op0)
+                for c in cands:
+                    fuse_module(module, as_meta(metas), **{kw: c})
         print("compiled", d.flush(), "kernel variants")
         return
     if not torch.cuda.is_available():
@@ -117,25 +197,29 @@ def main(argv=None):
     dev = torch.device("cuda:0")
     entries = {}
     for name, (module, metas) in specs.items():
-        _, op0 = fuse_module(module, metas)
-        inputs = [random_like(m, dev) for m in metas]
+        _, op0 = fuse_module(module, as_meta(metas))
+        kw, cands, fields = node_candidates(op0)
+        # real tensors where the spec carries them (a CSR structure cannot be random), else random
+        inputs = [m.to(dev) if m.device.type != "meta" else random_like(m, dev) for m in metas]
         rows = []
-        for c in candidates(op0):
-            gm, op = fuse_module(module, metas, tile=c)
+        for c in cands:
+            gm, op = fuse_module(module, as_meta(metas), **{kw: c})
             us = statistics.median(op.time_kernel(fused_args(gm, op, inputs), iters=a.iters)) * 1e3
             op.check_status()
-            rows.append((us, op.tile))
-        default_us, default_tile = rows[0]          # candidates() lists the closed-form choice first
+            used = op.tile if kw in ("tile", "conv_tile") else op.cfg
+            rows.append((us, used))
+        default_us, default_cfg = rows[0]           # the candidate lists start with the closed-form choice
         rows.sort(key=lambda r: r[0])
         us, t = rows[0]
         if us > a.min_gain * default_us:
-            us, t = default_us, default_tile           # within noise of the default: keep the default
-        if t is not default_tile:       # the table only lists departures from the closed-form choice
-            entries[op0.tune_key] = dict(bn=t.bn, stages=t.stages, epi_warps=t.epi_warps, split_k=t.split_k,
-                                         cta_pair=int(t.cta_pair), node=name, us=round(us, 1),
+            us, t = default_us, default_cfg            # within noise of the default: keep the default
+        desc = lambda c: [int(getattr(c, f)) for f in fields]
+        if t is not default_cfg:        # the table only lists departures from the closed-form choice
+            entries[op0.tune_key] = dict({f: int(getattr(t, f)) for f in fields}, node=name, us=round(us, 1),
                                          default_us=round(default_us, 1))
-        desc = lambda c: [c.bn, c.stages, c.epi_warps, c.split_k, int(c.cta_pair)]
-        print(json.dumps(dict(node=name, best=desc(t), us=round(us, 1), tflops=round(op0.flops / us / 1e6, 1),
+        rate = {"tflops": round(op0.flops / us / 1e6, 1)} if getattr(op0, "flops", 0) else \
+               ({"gbs": round(op0.bytes_moved / us / 1e3, 1)} if hasattr(op0, "bytes_moved") else {})
+        print(json.dumps(dict(node=name, fields=list(fields), best=desc(t), us=round(us, 1), **rate,
                               all=[desc(r[1]) + [round(r[0], 1)] for r in rows])))
         sys.stdout.flush()
     tuning.save(entries, a.out)

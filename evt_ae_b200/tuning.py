@@ -1,4 +1,4 @@
-"""Measured tile choices for fused GEMMs.
+"""Measured kernel configurations for fused nodes.
 
 The reference picks its CUTLASS tile descriptions with a profile-guided tuner whose results
 live in a cache keyed by problem size and epilogue census
@@ -9,6 +9,12 @@ workload on the GPU and records the winner in `tuned_tiles.json` beside this fil
 `lookup()` is consulted by the fused-op constructors before the closed-form choice of
 `fused_ops.pick_gemm_tile`.  Keys hold the epilogue signature hash, the problem size, the
 operand majors and the dtype, so a table entry can never be applied to a different kernel.
+
+The other node kinds go through the same table with keys `row|...`, `conv|...`, `spmm|...`
+(`key_for_node`): threads per row / CTA size of the softmax and LayerNorm kernels (the reference's
+reduce-apply tuner, autotuner/reduce_apply_tuner.py:32-275), channel-tile width, ring depth and
+epilogue warps of the convolutions (autotuner/conv_tuner.py:27-147), and the row-length threshold,
+task length and unrolls of the SpMM.  `lookup_config` returns the stored fields as a dict.
 """
 from __future__ import annotations
 
@@ -26,6 +32,17 @@ _table: Optional[Dict[str, dict]] = None
 def key_for(ir, M: int, N: int, K: int, L: int, a_major: str, b_major: str, dtype) -> str:
     sig = hashlib.sha256(ir.signature().encode()).hexdigest()[:16]
     return f"{sig}|{L}x{M}x{N}x{K}|{a_major}{b_major}|{str(dtype).replace('torch.', '')}"
+
+
+def key_for_node(kind: str, ir, shape, dtype) -> str:
+    """Key of a row-kernel / convolution / SpMM node: kind, epilogue signature, problem shape, dtype."""
+    sig = hashlib.sha256(ir.signature().encode()).hexdigest()[:16]
+    return f"{kind}|{sig}|{'x'.join(str(int(s)) for s in shape)}|{str(dtype).replace('torch.', '')}"
+
+
+def lookup_config(key: str) -> Optional[dict]:
+    e = _load().get(key)
+    return dict(e) if e is not None else None
 
 
 def _load() -> Dict[str, dict]:

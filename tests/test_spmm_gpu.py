@@ -59,6 +59,26 @@ def test_sddmm(cuda_device):
     assert torch.allclose(out.double(), ref, rtol=1e-5, atol=1e-4)
 
 
+def test_sddmm_gcn_size(cuda_device):
+    """Edge scores on the GCN configuration's graph (169,343 nodes, 1.17 M stored entries, hub rows
+    of tens of thousands of entries), 128 features: sampled entries against a float64 dot product,
+    plus linearity in U as a check that does not depend on the oracle."""
+    n = 169343
+    r, c = P.chung_lu_graph(n, 585000)
+    crow, col = P.csr_reference(r, c, n)
+    u = P.seeded((n, 128), 95, 1.0, torch.float32)
+    v = P.seeded((n, 128), 96, 1.0, torch.float32)
+    dev = lambda t: t.to(cuda_device)
+    out = ops.sddmm(dev(crow), dev(col), dev(u), dev(v))
+    out2 = ops.sddmm(dev(crow), dev(col), dev(u) * 2, dev(v))
+    assert torch.allclose(out2, out * 2, rtol=1e-6, atol=1e-6)
+    out = out.cpu()
+    rows = torch.repeat_interleave(torch.arange(n), (crow[1:] - crow[:-1]).long())
+    pick = torch.cat([torch.arange(0, 30000), torch.arange(0, col.shape[0], 37)])      # hub rows and a spread
+    ref = (u.double()[rows[pick]] * v.double()[col.long()[pick]]).sum(-1)
+    assert torch.allclose(out[pick].double(), ref, rtol=1e-5, atol=1e-4)
+
+
 @pytest.mark.parametrize("n,edges", [(1000, 5000), (169343, 585000)])
 def test_csr_build_bit_exact(n, edges, cuda_device):
     r, c = P.chung_lu_graph(n, edges)

@@ -43,9 +43,17 @@ def test_table_round_trip_and_lookup(tmp_path, monkeypatch):
 def test_shipped_table_is_well_formed_and_explicit_tile_wins(tmp_path, monkeypatch):
     shipped = json.load(open(tuning.TABLE_PATH))
     for key, e in shipped.items():
-        assert e["bn"] in (32, 64, 128, 256) and e["epi_warps"] in (4, 8, 12, 16) and 2 <= e["stages"] <= 8
-        assert e.get("cta_pair", 0) in (0, 1) and e["split_k"] >= 1, key
         assert key.count("|") == 3
+        kind = key.split("|")[0]
+        if kind == "row":
+            assert e["tpr"] in (8, 16, 32, 64, 128, 256, 512, 1024) and e["threads"] % 32 == 0 and 1 <= e["vpt"] <= 8, key
+        elif kind == "spmm":
+            assert e["t_long"] > 0 and e["task_len"] >= 32 and e["u_short"] in (1, 2, 4, 8), key
+        elif kind.startswith("conv"):
+            assert e["bn"] in (64, 128, 256) and e["epi_warps"] in (8, 16) and 2 <= e["stages"] <= 8, key
+        else:
+            assert e["bn"] in (32, 64, 128, 256) and e["epi_warps"] in (4, 8, 12, 16) and 2 <= e["stages"] <= 8
+            assert e.get("cta_pair", 0) in (0, 1) and e["split_k"] >= 1, key
     mod, metas = workload_specs("config0")["config0"]
     _, op = fuse_module(mod, metas)
     path = str(tmp_path / "t.json")
@@ -68,3 +76,33 @@ def test_candidates_start_with_the_closed_form_choice_and_are_unique():
     assert (cands[0].bn, cands[0].split_k, cands[0].epi_warps, cands[0].cta_pair) == (base.bn, base.split_k, 8, base.cta_pair)
     sig = [(c.bn, c.epi_warps, c.split_k, c.cta_pair) for c in cands]
     assert len(sig) == len(set(sig)) and any(c.split_k == 1 for c in cands)
+
+
+def test_every_node_kind_has_candidates_and_a_table_entry_is_applied(tmp_path, monkeypatch):
+    """Row kernels, convolutions and SpMM go through the same table as the GEMMs."""
+    from evt_ae_b200.tune import node_candidates
+    from evt_ae_b200 import codegen
+    row = P.softmax_plain(256, 512, torch.float16)
+    conv = P.conv_fprop_bn_stat(4, 28, 28, 128, 256, 3, 1)
+    sp = P.spmm_case(2000, 9000, 128, "sym")
+    entries = {}
+    for case, kw_expected in ((row, "row_config"), (conv, "conv_tile"), (sp, "spmm_config")):
+        _, op = fuse_module(case.module, _meta(case))
+        kw, cands, fields = node_candidates(op)
+        assert kw == kw_expected and len(cands) >= 3
+        pick = cands[-1]
+        entries[op.tune_key] = {f: int(getattr(pick, f)) for f in fields}
+    path = str(tmp_path / "t.json")
+    tuning.save(entries, path)
+    monkeypatch.setattr(tuning, "TABLE_PATH", path)
+    monkeypatch.setattr(tuning, "_table", None)
+    for case in (row, conv, sp):
+        _, op = fuse_module(case.module, _meta(case))
+        e = entries[op.tune_key]
+        cfg = op.tile if hasattr(op, "geom") else op.cfg
+        for f, v in e.items():
+            if f == "stages":       # the ring is shortened when the staging tiles need the shared memory
+                assert int(getattr(cfg, f)) <= v, (case.name, f)
+            else:
+                assert int(getattr(cfg, f)) == v, (case.name, f)
+    monkeypatch.setattr(tuning, "_table", None)
