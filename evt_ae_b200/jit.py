@@ -4,7 +4,9 @@ The reference JIT-compiles every fused kernel through the CUTLASS Python compile
 the binaries in `compiled_cache.db` (python/gtl/compiler/passes/evt_fuser.py:738-746;
 python/gtl/ops/reduce_apply_operation.py:120-136).  Here each translation unit is compiled
 by nvcc for sm_100a into `evt_ae_b200/_kcache/<hash>.cubin`; the hash covers the generated
-source and the hand-written headers it includes, so editing a kernel invalidates the cache.
+source and the hand-written headers it includes, so editing a kernel invalidates the cache
+(images built from older headers are never picked up again; `prune()` removes them, least
+recently used first, when the directory outgrows a budget).
 """
 from __future__ import annotations
 
@@ -72,6 +74,10 @@ def compile_cubin(source: str, verbose: bool = False) -> str:
     """Returns the path of the cubin for `source`, compiling it if it is not cached."""
     path = cubin_path_for(source)
     if os.path.exists(path):
+        try:
+            os.utime(path)          # marks the image as recently used for prune()
+        except OSError:
+            pass
         return path
     if _pending is not None:
         _pending.append(source)
@@ -105,3 +111,36 @@ def compile_many(sources: Iterable[str], workers: int = 8) -> List[str]:
     sources = list(sources)
     with ThreadPoolExecutor(max_workers=workers) as ex:
         return list(ex.map(compile_cubin, sources))
+
+
+def cache_entries() -> List[Tuple[str, float, int]]:
+    """(key, last use, bytes incl. the kept source and compiler log) of every cached image."""
+    out = []
+    if not os.path.isdir(CACHE_DIR):
+        return out
+    for f in os.listdir(CACHE_DIR):
+        if f.endswith(".cubin"):
+            p = os.path.join(CACHE_DIR, f)
+            size = sum(os.path.getsize(q) for q in (p, p + ".cu", p + ".log") if os.path.exists(q))
+            out.append((f[:-6], os.path.getmtime(p), size))
+    return out
+
+
+def prune(max_bytes: int) -> int:
+    """Removes least recently used images (with their sources and logs) until the cache holds at
+    most `max_bytes`; returns the number of images removed.  Anything removed is rebuilt on its
+    next use."""
+    entries = sorted(cache_entries(), key=lambda e: e[1])
+    total = sum(e[2] for e in entries)
+    removed = 0
+    with _lock:
+        for key, _, size in entries:
+            if total <= max_bytes:
+                break
+            base = os.path.join(CACHE_DIR, key + ".cubin")
+            for q in (base, base + ".cu", base + ".log"):
+                if os.path.exists(q):
+                    os.remove(q)
+            total -= size
+            removed += 1
+    return removed
