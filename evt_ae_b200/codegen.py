@@ -817,6 +817,38 @@ class ConvTileConfig:
         return 64 + 32 * self.epi_warps
 
 
+def conv_wgrad_source(ir: EpilogueIR, dtype: torch.dtype, cfg: GemmTileConfig) -> Tuple[str, EpilogueSource, str]:
+    """Translation unit for a convolution weight gradient: the GEMM kernel (one CTA per tile, both
+    operands MN-major, split along the reduction) with its operand tiles fetched as boxes of the two
+    channels-last tensors.  The epilogue sees the [K, R*S*C] result matrix."""
+    cfg.cta_pair, cfg.row_resident = False, False
+    epi = EpilogueGenerator(ir, row_tile=128, staged=cfg.staged, tma_store=cfg.tma_store and cfg.staged).generate()
+    cfg.stage_tiles = epi.stage_tiles
+    while cfg.stages > 2 and gemm_smem_bytes(cfg) > 227 * 1024:
+        cfg.stages -= 1
+    bf16 = "true" if dtype == torch.bfloat16 else "false"
+    body = f"""// generated by evt_ae_b200.codegen -- do not edit
+{DEBUG_DEFINE()}#include "gemm_sm100.cuh"
+#include "epilogue_ops.cuh"
+using namespace evtb;
+
+{epi.struct_code}
+
+using Cfg = GemmConfig<{cfg.bn}, {cfg.stages}, true, true, {bf16}, {cfg.epi_warps}, {cfg.stage_tiles * 2048}, {'true' if cfg.split_k > 1 else 'false'}, false, true>;
+
+extern "C" __global__ void __launch_bounds__(Cfg::THREADS, 1)
+evtb_gemm_kernel(const __grid_constant__ GemmParams p) {{
+  gemm_kernel_body<Cfg, Epi>(p);
+}}
+
+extern "C" __global__ void evtb_kernel_info(int* out) {{
+  out[0] = Cfg::SMEM_BYTES;
+  out[1] = Cfg::THREADS;
+}}
+"""
+    return body, epi, "evtb_gemm_kernel"
+
+
 def conv_smem_bytes(cfg: ConvTileConfig) -> int:
     return 1024 + cfg.stages * (128 * 64 * 2 + cfg.bn * 64 * 2) + 1024 + cfg.epi_warps * cfg.stage_tiles * 2048
 

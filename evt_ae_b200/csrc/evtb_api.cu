@@ -342,6 +342,8 @@ struct evtb_plan {
   void* profile_buffer = nullptr;
   // convolution: everything of ConvParams that does not depend on the operand addresses
   evtb::ConvParams conv{};
+  // convolution weight gradient
+  evtb::WgradGeom wg{};
   // SpMM
   CUfunction prep_fn = nullptr;
   int t_long = 0, task_len = 0, max_tasks = 0, long_ctas = 0, prep_grid = 0;
@@ -374,7 +376,7 @@ int evtb_plan_create(const evtb_desc* desc, evtb_plan** out) {
   }
   *out = nullptr;
   const evtb_desc& d = *desc;
-  if (d.kind < EVTB_GEMM || d.kind > EVTB_CONV_DGRAD) {
+  if (d.kind < EVTB_GEMM || d.kind > EVTB_CONV_WGRAD) {
     set_error("unknown plan kind");
     return EVTB_EINVAL;
   }
@@ -554,6 +556,62 @@ int evtb_plan_create(const evtb_desc* desc, evtb_plan** out) {
       p->partial_bytes = sizeof(float) * static_cast<size_t>(tiles) * p->splits * evtb::kBM * d.tile_n;
       p->workspace = p->partial_bytes + sizeof(unsigned int) * static_cast<size_t>(tiles);
     }
+  } else if (d.kind == EVTB_CONV_WGRAD) {
+    p->main_operands = 2;
+    const evtb_conv& g = d.conv;
+    const char* bad = nullptr;
+    if (d.dtype != EVTB_F16 && d.dtype != EVTB_BF16) bad = "weight gradient: operands must be f16 or bf16";
+    else if (g.N <= 0 || g.H <= 0 || g.W <= 0 || g.C <= 0 || g.K <= 0 || g.R <= 0 || g.S <= 0 || g.P <= 0 || g.Q <= 0 ||
+             g.stride_h <= 0 || g.stride_w <= 0 || g.dil_h <= 0 || g.dil_w <= 0 || g.pad_h < 0 || g.pad_w < 0)
+      bad = "weight gradient: non-positive geometry";
+    else if (g.P != (g.H + 2 * g.pad_h - g.dil_h * (g.R - 1) - 1) / g.stride_h + 1 ||
+             g.Q != (g.W + 2 * g.pad_w - g.dil_w * (g.S - 1) - 1) / g.stride_w + 1)
+      bad = "weight gradient: P, Q do not match H, W, filter, padding and stride";
+    else if (g.C % 64 != 0 || g.K % 8 != 0) bad = "weight gradient: C must be a multiple of 64 and K of 8";
+    else if ((d.tile_n != 64 && d.tile_n != 128 && d.tile_n != 256) || g.C % d.tile_n != 0)
+      bad = "weight gradient: tile_n must be 64, 128 or 256 and divide C";
+    else if (d.M != g.K || d.N != 1ll * g.R * g.S * g.C) bad = "weight gradient: M must be K and N must be R*S*C";
+    else if (d.stages < 2 || d.stages > 8) bad = "weight gradient: 2 <= stages <= 8";
+    else if (d.n_tma_stores < 0 || d.n_tma_stores > evtb::kMaxTmaStores) bad = "weight gradient: at most 4 TMA-stored results";
+    if (bad != nullptr) {
+      set_error(bad);
+      drv.ModuleUnload(p->module);
+      delete p;
+      return EVTB_EINVAL;
+    }
+    evtb::WgradGeom& w = p->wg;
+    w.S = g.S; w.C = g.C;
+    w.stride_h = g.stride_h; w.stride_w = g.stride_w; w.pad_h = g.pad_h; w.pad_w = g.pad_w;
+    w.dil_h = g.dil_h; w.dil_w = g.dil_w;
+    // the box of 64 output positions that covers N x P x Q with the fewest boxes (ties: widest rows)
+    long long best = -1;
+    for (int bq = 64; bq >= 1; bq /= 2)
+      for (int bp = 64 / bq; bp >= 1; bp /= 2) {
+        const int bn = 64 / (bq * bp);
+        if (bq * g.stride_w > 256 || bp * g.stride_h > 256) continue;
+        const long long boxes = 1ll * ceil_div(g.Q, bq) * ceil_div(g.P, bp) * ceil_div(g.N, bn);
+        if (best < 0 || boxes < best) {
+          best = boxes;
+          w.bq = bq; w.bp = bp; w.bn = bn;
+        }
+      }
+    w.boxes_w = ceil_div(g.Q, w.bq);
+    w.boxes_h = ceil_div(g.P, w.bp);
+    w.boxes_n = ceil_div(g.N, w.bn);
+    p->tiles_m = static_cast<int>((d.M + evtb::kBM - 1) / evtb::kBM);
+    p->tiles_n = static_cast<int>(d.N / d.tile_n);
+    const long long tiles = 1ll * p->tiles_m * p->tiles_n;
+    const int num_k = static_cast<int>(best);
+    p->splits = d.split_k > 1 ? d.split_k : 1;
+    if (p->splits > num_k) p->splits = num_k;
+    p->kb_per_split = (num_k + p->splits - 1) / p->splits;
+    p->splits = (num_k + p->kb_per_split - 1) / p->kb_per_split;
+    const long long units = tiles * p->splits;
+    p->grid = static_cast<int>(units < p->sm_count ? units : p->sm_count);
+    if (p->splits > 1) {
+      p->partial_bytes = sizeof(float) * static_cast<size_t>(tiles) * p->splits * evtb::kBM * d.tile_n;
+      p->workspace = p->partial_bytes + sizeof(unsigned int) * static_cast<size_t>(tiles);
+    }
   } else if (d.kind == EVTB_CONV_FPROP || d.kind == EVTB_CONV_DGRAD) {
     p->main_operands = 2;
     int rc = (d.dtype == EVTB_F16 || d.dtype == EVTB_BF16) ? plan_convolution(d, p->conv, &p->grid, p->sm_count)
@@ -718,6 +776,47 @@ int evtb_launch_ex(evtb_plan* plan, const void* const* ptrs, int n, void* worksp
     CUresult r = drv.LaunchKernel(plan->fn, plan->grid, 1, 1, d.threads, 1, 1, d.smem_bytes,
                                   static_cast<CUstream>(stream), args, nullptr);
     if (r != CUDA_SUCCESS) return cu_fail("cuLaunchKernel(gemm)", r);
+    return EVTB_OK;
+  }
+
+  if (d.kind == EVTB_CONV_WGRAD) {
+    const evtb_conv& g = d.conv;
+    evtb::GemmParams p;
+    std::memset(&p, 0, sizeof(p));
+    p.wg = plan->wg;
+    int rc = encode_activation_map(&p.tma_a, ptrs[0], g.K, g.Q, g.P, g.N, p.wg.bq, p.wg.bp, p.wg.bn, 1, 1);
+    if (rc != EVTB_OK) return rc;
+    rc = encode_activation_map(&p.tma_b, ptrs[1], g.C, g.W, g.H, g.N, p.wg.bq, p.wg.bp, p.wg.bn, g.stride_w, g.stride_h);
+    if (rc != EVTB_OK) return rc;
+    p.M = static_cast<int>(d.M);
+    p.N = static_cast<int>(d.N);
+    p.K = g.N * g.P * g.Q;
+    p.L = 1;
+    p.tiles_m = plan->tiles_m;
+    p.tiles_n = plan->tiles_n;
+    p.num_tiles = plan->tiles_m * plan->tiles_n;
+    p.status = static_cast<int*>(status_word);
+    p.prof = nullptr;
+    for (int i = 0; i < d.n_tma_stores; ++i) {
+      const evtb_tma_store& ts = d.tma_stores[i];
+      rc = encode_store_map(&epi.tmap[i], epi.ptr[ts.slot], d.N, d.M, 1, ts.stride_row, ts.stride_batch);
+      if (rc != EVTB_OK) return rc;
+    }
+    p.epi = epi;
+    p.splits = plan->splits;
+    p.kb_per_split = plan->kb_per_split;
+    if (plan->splits > 1) {
+      if (workspace == nullptr || (reinterpret_cast<uintptr_t>(workspace) & 15u) != 0) {
+        set_error("split weight-gradient plan needs a 16-byte aligned workspace of evtb_plan_workspace_bytes() bytes");
+        return EVTB_EINVAL;
+      }
+      p.partial = static_cast<float*>(workspace);
+      p.tile_counters = reinterpret_cast<unsigned int*>(static_cast<char*>(workspace) + plan->partial_bytes);
+    }
+    void* args[1] = {&p};
+    CUresult r = drv.LaunchKernel(plan->fn, plan->grid, 1, 1, d.threads, 1, 1, d.smem_bytes,
+                                  static_cast<CUstream>(stream), args, nullptr);
+    if (r != CUDA_SUCCESS) return cu_fail("cuLaunchKernel(convolution weight gradient)", r);
     return EVTB_OK;
   }
 

@@ -34,9 +34,23 @@ struct alignas(64) EpiParams {
   unsigned long long rng_offset;
 };
 
+// Convolution weight gradient run as a GEMM: dW[k, (r, s, c)] = sum over output positions of
+// dy[position, k] * x[position shifted by tap (r, s), c].  Rows are output channels, columns the
+// R*S*C filter entries of an output channel, the reduction runs over boxes of 64 output positions
+// (bq x bp x bn) that TMA fetches from the two 4-D channels-last tensors: dy at the box itself, x at
+// the box moved by the column tile's tap, strided by the convolution stride, zero-filled in the
+// padding.  Both operand tiles arrive MN-major (channels contiguous).
+struct WgradGeom {
+  int bq, bp, bn;                  // box of 64 output positions
+  int boxes_w, boxes_h, boxes_n;   // boxes along q, p, n: their product is the reduction length in k-blocks
+  int S, C;                        // filter width; channels per tap (a column tile lies inside one tap)
+  int stride_h, stride_w, pad_h, pad_w, dil_h, dil_w;
+};
+
 struct alignas(64) GemmParams {
   CUtensorMap tma_a;  // K-major: dims (K, M, L), box (64, 128, 1); MN-major: dims (M, K, L), box (64, 64, 1)
   CUtensorMap tma_b;  // K-major: dims (K, N, L), box (64, BN, 1); MN-major: dims (N, K, L), box (64, 64, 1)
+                      // weight gradient: a = dy dims (K, Q, P, N), b = x dims (C, W, H, N), boxes of 64 channels x 64 positions
   int M, N, K, L;
   int tiles_m, tiles_n, num_tiles;
   // split-K: a tile's K range is cut into `splits` units of `kb_per_split` k-blocks; every
@@ -51,6 +65,7 @@ struct alignas(64) GemmParams {
   // waiting for a free slot, [2] MMA issuer waiting for data, [3] MMA issuer waiting for a
   // free accumulator, [4] epilogue (warp 2) waiting for an accumulator, [5] epilogue working
   long long* prof;
+  WgradGeom wg;       // weight-gradient kernels only
   EpiParams epi;
 };
 
@@ -107,8 +122,10 @@ __device__ __forceinline__ bool epi_in_bounds(const EpiCtx& c, long long off, in
 #endif
 
 template <int BN_, int STAGES_, bool A_MN_, bool B_MN_, bool BF16_, int EPI_WARPS_ = 8, int EPI_STAGE_BYTES_ = 0,
-          bool SPLIT_K_ = false, bool K_ROTATE_ = false>
+          bool SPLIT_K_ = false, bool K_ROTATE_ = false, bool WGRAD_ = false>
 struct GemmConfig {
+  static constexpr bool WGRAD = WGRAD_;      // operands are boxes of two 4-D convolution tensors (needs A_MN and B_MN)
+  static_assert(!WGRAD_ || (A_MN_ && B_MN_ && BN_ % 64 == 0), "weight gradient: both operands MN-major, BN % 64 == 0");
   static constexpr bool SPLIT_K = SPLIT_K_;
   static constexpr bool K_ROTATE = K_ROTATE_;
   // bytes of shared-memory staging tiles each epilogue warp owns (a multiple of 2048)
@@ -198,6 +215,17 @@ __device__ __forceinline__ int rotated_kb(int i, int kb0, int kb1, int rot) {
   return kb0 + j;
 }
 
+__device__ __forceinline__ void tma_load_4d_box(void* smem_dst, const CUtensorMap* map, uint64_t* bar,
+                                                int c0, int c1, int c2, int c3) {
+  asm volatile(
+      "cp.async.bulk.tensor.4d.shared::cta.global.mbarrier::complete_tx::bytes"
+      " [%0], [%1, {%3, %4, %5, %6}], [%2];"
+      :
+      : "r"(smem_u32(smem_dst)), "l"(reinterpret_cast<uint64_t>(map)), "r"(smem_u32(bar)), "r"(c0),
+        "r"(c1), "r"(c2), "r"(c3)
+      : "memory");
+}
+
 __device__ __forceinline__ void epi_bar_sync(int nthreads) {
   asm volatile("bar.sync 1, %0;" ::"r"(nthreads) : "memory");
 }
@@ -271,7 +299,7 @@ __device__ __forceinline__ void gemm_kernel_body(const GemmParams& p) {
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
-  const int num_k = (p.K + kBK - 1) / kBK;
+  const int num_k = Cfg::WGRAD ? p.wg.boxes_w * p.wg.boxes_h * p.wg.boxes_n : (p.K + kBK - 1) / kBK;
   const int num_units = Cfg::SPLIT_K ? p.num_tiles * p.splits : p.num_tiles;
 #ifdef EVTB_PROFILE
   const long long prof_start = clock64();
@@ -340,14 +368,31 @@ __device__ __forceinline__ void gemm_kernel_body(const GemmParams& p) {
           uint8_t* sb = sa + Cfg::A_BYTES;
           mbar_arrive_expect_tx(&hdr->full[s], Cfg::STAGE_BYTES);
           const int k0 = kb * kBK;
-          if constexpr (!Cfg::A_MN) {
+          if constexpr (Cfg::WGRAD) {
+            // k-block = box of 64 output positions; the column tile picks the filter tap
+            const WgradGeom& g = p.wg;
+            const int q0 = (kb % g.boxes_w) * g.bq;
+            const int p0 = ((kb / g.boxes_w) % g.boxes_h) * g.bp;
+            const int i0 = (kb / (g.boxes_w * g.boxes_h)) * g.bn;
+            const int tap = n0 / g.C, c0 = n0 - tap * g.C;
+            const int dh = (tap / g.S) * g.dil_h - g.pad_h, dw = (tap % g.S) * g.dil_w - g.pad_w;
+#pragma unroll
+            for (int c = 0; c < kBM / 64; ++c)
+              tma_load_4d_box(sa + c * (kBK * 128), &p.tma_a, &hdr->full[s], m0 + c * 64, q0, p0, i0);
+#pragma unroll
+            for (int c = 0; c < Cfg::BN / 64; ++c)
+              tma_load_4d_box(sb + c * (kBK * 128), &p.tma_b, &hdr->full[s], c0 + c * 64, q0 * g.stride_w + dw,
+                              p0 * g.stride_h + dh, i0);
+          } else if constexpr (!Cfg::A_MN) {
             tma_load_3d(sa, &p.tma_a, &hdr->full[s], k0, m0, l);
           } else {
 #pragma unroll
             for (int c = 0; c < kBM / 64; ++c)
               tma_load_3d(sa + c * (kBK * 128), &p.tma_a, &hdr->full[s], m0 + c * 64, k0, l);
           }
-          if constexpr (!Cfg::B_MN) {
+          if constexpr (Cfg::WGRAD) {
+            // both operands were fetched above
+          } else if constexpr (!Cfg::B_MN) {
             tma_load_3d(sb, &p.tma_b, &hdr->full[s], k0, n0, l);
           } else {
 #pragma unroll

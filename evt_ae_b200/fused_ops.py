@@ -754,6 +754,94 @@ class FusedConvDgrad(_FusedConvBase):
     dgrad = True
 
 
-FUSED_CLASSES = {"conv_fprop": FusedConvFprop, "conv_dgrad": FusedConvDgrad, "spmm": FusedSpmm, "gemm": FusedGEMM, "bmm": FusedBMM, "softmax": FusedSoftmax,
+class FusedConvWgrad(FusedOpBase):
+    """epilogue(conv_backward_weight(dy, x)) as the [K, R*S*C] matrix of the channels-last filter
+    gradient; operands [dy (N,P,Q,K), x (N,H,W,C)].  The reference leaves this leaf to cuDNN
+    (convolution_backward_weight_channel_last, pass_decomposition.py:92-107); here it is an implicit
+    GEMM over boxes of output positions, cut along that reduction so that every SM has a share."""
+    __name__ = "evt_b200_conv2d_wgrad_with_visitor"
+    target = "convolution_backward_weight_channel_last"
+
+    def __init__(self, trace: PartitionTrace, tile: Optional[GemmTileConfig] = None):
+        super().__init__(trace)
+        a = trace.attrs
+        dy, x = self.args
+        self.dtype = _dtype(dy)
+        if self.dtype not in (torch.float16, torch.bfloat16) or _dtype(x) != self.dtype:
+            raise NotImplementedError(f"convolution operands must both be fp16 or bf16, got {self.dtype}/{_dtype(x)}")
+        if a["groups"] != 1 or a["transposed"]:
+            raise NotImplementedError("grouped / transposed convolutions are not fused")
+        K, R, S, C = a["filter_shape"]
+        N, P, Q, K2 = _shape(dy)
+        N2, H, W, C2 = _shape(x)
+        if K2 != K or C2 != C or N2 != N:
+            raise ValueError("convolution operand shapes do not agree")
+        if C % 64 or K % 8:
+            raise NotImplementedError("the fused weight gradient needs C % 64 == 0 and K % 8 == 0 "
+                                      "(the 3-channel stem stays a library call)")
+        self.geom = dict(N=N, H=H, W=W, C=C, K=K, R=R, S=S, P=P, Q=Q, stride_h=a["stride"][0], stride_w=a["stride"][1],
+                         pad_h=a["padding"][0], pad_w=a["padding"][1], dil_h=a["dilation"][0], dil_w=a["dilation"][1])
+        import copy
+        self.tune_key = tuning.key_for_node("conv_wgrad", self.ir, [N, H, W, C, K, R, S, a["stride"][0], a["padding"][0]], self.dtype)
+        if tile is not None:
+            self.tile = copy.copy(tile)
+        else:
+            e = tuning.lookup_config(self.tune_key)
+            bn = int(e["bn"]) if e else (256 if C % 256 == 0 else 128 if C % 128 == 0 else 64)
+            tiles = ((K + 127) // 128) * (R * S * C // bn)
+            boxes = max(1, (N * P * Q) // 64)
+            split = int(e["split_k"]) if e else max(1, min(_sm_count() // max(tiles, 1), boxes // 8, 64))
+            self.tile = GemmTileConfig(bn=bn, stages=int(e["stages"]) if e else 6, epi_warps=int(e["epi_warps"]) if e else 8,
+                                       split_k=split)
+        if C % self.tile.bn:
+            raise ValueError("the weight-gradient tile width must divide C")
+        src, epi, entry = codegen.conv_wgrad_source(self.ir, self.dtype, self.tile)
+        self.source = src
+        self.slots = epi.slots
+        self.uses_rand = epi.uses_rand
+        self.image = jit.compile_cubin(src)
+        d = runtime.evtb_desc()
+        d.kind = runtime.EVTB_CONV_WGRAD
+        d.dtype = _DT[self.dtype]
+        d.M, d.N, d.K, d.L = K, R * S * C, N * P * Q, 1
+        d.tile_n = self.tile.bn
+        d.stages = self.tile.stages
+        d.threads = self.tile.threads
+        d.smem_bytes = codegen.gemm_smem_bytes(self.tile)
+        d.n_epilogue_ptrs = len(self.slots)
+        d.image_path = self.image.encode()
+        d.entry = entry.encode()
+        d.split_k = self.tile.split_k
+        d.n_tma_stores = len(epi.tma_stores)
+        for i, ts in enumerate(epi.tma_stores):
+            d.tma_stores[i].slot, d.tma_stores[i].stride_row, d.tma_stores[i].stride_batch = ts.slot, ts.stride_row, ts.stride_batch
+        for k, v in self.geom.items():
+            setattr(d.conv, k, int(v))
+        self.desc = d
+        self.plan = runtime.Plan(d) if torch.cuda.is_available() else None
+        self._workspace = None
+
+    def _workspace_ptr(self, device) -> int:
+        if self.plan is None or self.plan.workspace_bytes == 0:
+            return 0
+        if self._workspace is None or self._workspace.device != device:
+            self._workspace = torch.zeros((self.plan.workspace_bytes + 3) // 4, dtype=torch.int32, device=device)
+        return self._workspace.data_ptr()
+
+    @property
+    def flops(self) -> float:
+        g = self.geom
+        return 2.0 * g["N"] * g["P"] * g["Q"] * g["K"] * g["C"] * g["R"] * g["S"]
+
+    def _main_ptrs(self, main_tensors, keep):
+        if self.plan is None:
+            raise RuntimeError("no CUDA device: the fused weight gradient has no CPU path")
+        dy, x = main_tensors
+        if dy.dtype != self.dtype or x.dtype != self.dtype:
+            raise RuntimeError(f"convolution operand dtype {dy.dtype}/{x.dtype} != {self.dtype}")
+        return [dy.data_ptr(), x.data_ptr()]
+
+
+FUSED_CLASSES = {"conv_fprop": FusedConvFprop, "conv_dgrad": FusedConvDgrad, "conv_wgrad": FusedConvWgrad, "spmm": FusedSpmm, "gemm": FusedGEMM, "bmm": FusedBMM, "softmax": FusedSoftmax,
                  "softmax_backward": FusedSoftmaxBackward, "layernorm": FusedLayerNorm,
                  "layernorm_backward": FusedLayerNormBackward}

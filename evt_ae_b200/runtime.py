@@ -16,7 +16,7 @@ HERE = os.path.dirname(os.path.abspath(__file__))
 LIB_PATH = os.path.join(HERE, "libevt_b200.so")
 
 (EVTB_GEMM, EVTB_BGEMM, EVTB_SOFTMAX, EVTB_SOFTMAX_BWD, EVTB_LAYERNORM, EVTB_LAYERNORM_BWD, EVTB_SPMM,
- EVTB_CONV_FPROP, EVTB_CONV_DGRAD) = range(9)
+ EVTB_CONV_FPROP, EVTB_CONV_DGRAD, EVTB_CONV_WGRAD) = range(10)
 EVTB_F16, EVTB_BF16, EVTB_F32 = range(3)
 EVTB_MAJOR_K, EVTB_MAJOR_MN = 0, 1
 

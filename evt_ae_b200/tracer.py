@@ -38,6 +38,7 @@ ANCHOR_OPS = {
     "spmm_sym": "spmm",
     "convolution_forward_channel_last": "conv_fprop",
     "convolution_backward_data_channel_last": "conv_dgrad",
+    "convolution_backward_weight_channel_last": "conv_wgrad",
 }
 
 ROW_EPILOGUE_OPS = {"_softmax": "softmax", "_softmax_backward_data": "softmax_backward"}
@@ -426,6 +427,8 @@ class _Tracer:
             L, M, N = shape
         elif self.kind == "spmm":
             L, M, N = 1, int(math.prod(shape[:-1])), shape[-1]
+        elif self.kind == "conv_wgrad":     # [K, R, S, C] filter gradient = the [K, R*S*C] matrix
+            L, M, N = 1, shape[0], int(math.prod(shape[1:]))
         else:  # reduce-apply: rows x last dim
             L, M, N = 1, int(math.prod(shape[:-1])), shape[-1]
         self.ir = EpilogueIR(L, M, N)
@@ -484,6 +487,8 @@ class _Tracer:
             mainloop_args = [a.args[0], a.args[1]]            # (x, w, stride, padding, dilation, ...)
         elif self.kind == "conv_dgrad":
             mainloop_args = [a.args[0], a.args[2]]            # (dy, x [shape only], w, stride, ...)
+        elif self.kind == "conv_wgrad":
+            mainloop_args = [a.args[0], a.args[1]]            # (dy, x, w [shape only], stride, ...)
         else:
             mainloop_args = [x for x in a.args if isinstance(x, FxNode)]
         if self.kind in ("softmax", "softmax_backward"):
@@ -533,7 +538,7 @@ class _Tracer:
                      and n not in aux_getitems.values() and n.op == "call_function"]
 
         # reduce-apply kernels never carry reductions (evt_fuser.py:1096-1100)
-        if self.kind not in ("gemm", "bmm", "conv_fprop", "conv_dgrad"):
+        if self.kind not in ("gemm", "bmm", "conv_fprop", "conv_dgrad", "conv_wgrad"):
             epi_nodes = [n for n in epi_nodes if op_name(n.target) not in ("sum", "amax")]
         epi_set = set(epi_nodes)
 
@@ -598,7 +603,7 @@ class _Tracer:
         for n in list(accum_nodes) + epi_nodes:
             if any(u not in epi_set and u is not a and u not in accum_nodes for u in n.users):
                 outputs.append(n)
-        if self.kind in ("gemm", "bmm", "spmm", "softmax", "softmax_backward", "conv_fprop", "conv_dgrad") and not epi_nodes:
+        if self.kind in ("gemm", "bmm", "spmm", "softmax", "softmax_backward", "conv_fprop", "conv_dgrad", "conv_wgrad") and not epi_nodes:
             outputs = [a]
         # keep graph order
         order = {n: i for i, n in enumerate(self.gm.graph.nodes)}
@@ -631,13 +636,15 @@ class _Tracer:
             attrs["row_resident"] = True
         if self.kind == "spmm":
             attrs["fused_norm"] = op_name(a.target) == "spmm_sym"
-        if self.kind in ("conv_fprop", "conv_dgrad"):
+        if self.kind in ("conv_fprop", "conv_dgrad", "conv_wgrad"):
             off = 2 if self.kind == "conv_fprop" else 3
             attrs["stride"], attrs["padding"], attrs["dilation"] = (list(a.args[off]), list(a.args[off + 1]),
                                                                     list(a.args[off + 2]))
             attrs["transposed"], attrs["groups"] = bool(a.args[off + 3]), int(a.args[off + 5])
             if self.kind == "conv_dgrad":
                 attrs["input_shape"] = tuple(_shape(a.args[1]))
+            if self.kind == "conv_wgrad":
+                attrs["filter_shape"] = tuple(_shape(a.args[2]))
         if tuple_anchor:
             attrs["aux_getitems"] = aux_getitems
         if self.kind == "layernorm":

@@ -575,9 +575,10 @@ def small_spmm_cases():
 # decomposition pass (channels-last leaves, batch norm split into statistics + apply,
 # pass_decomposition.py:66-189, evt_fuser.py:1258-1302); batch sizes reduced where noted.
 from evt_ae_b200.ops import (convolution_backward_data_channel_last,      # noqa: E402
-                             convolution_forward_channel_last)
+                             convolution_backward_weight_channel_last, convolution_forward_channel_last)
 torch.fx.wrap("convolution_forward_channel_last")
 torch.fx.wrap("convolution_backward_data_channel_last")
+torch.fx.wrap("convolution_backward_weight_channel_last")
 
 
 def conv_fprop_bn_stat(N, H, W, C, K, R, stride, dtype=torch.float16):
@@ -639,6 +640,27 @@ def conv_dgrad_strided(N, H, W, C, K, R, stride, dtype=torch.float16):
     return Case(f"conv_dgrad_strided_{N}x{H}x{W}x{C}_k{K}_r{R}_s{stride}_{str(dtype)[6:]}", Mod(),
                 [seeded((N, P_, Q_, K), 49, 1.0, dtype), seeded((N, H, W, C), 50, 1.0, dtype),
                  seeded((K, R, R, C), 51, 0.05, dtype)])
+
+
+def conv_wgrad_plain(N, H, W, C, K, R, stride, dtype=torch.float16):
+    """filter gradient of a channels-last convolution, dW [K, R, R, C] (the reference's leaf
+    convolution_backward_weight_channel_last, pass_decomposition.py:92-107)."""
+    pad = R // 2
+    P_ = (H + 2 * pad - R) // stride + 1
+    Q_ = (W + 2 * pad - R) // stride + 1
+
+    class Mod(torch.nn.Module):
+        def forward(self, dy, x, w):
+            return convolution_backward_weight_channel_last(dy, x, w, [stride, stride], [pad, pad], [1, 1], False, [0, 0], 1)
+    return Case(f"conv_wgrad_{N}x{H}x{W}x{C}_k{K}_r{R}_s{stride}_{str(dtype)[6:]}", Mod(),
+                [seeded((N, P_, Q_, K), 52, 0.25, dtype), seeded((N, H, W, C), 53, 1.0, dtype),
+                 seeded((K, R, R, C), 54, 0.05, dtype)])
+
+
+def small_conv_wgrad_cases():
+    return [conv_wgrad_plain(4, 14, 14, 64, 64, 3, 1), conv_wgrad_plain(3, 9, 11, 128, 192, 3, 1),
+            conv_wgrad_plain(4, 28, 28, 128, 256, 3, 2), conv_wgrad_plain(2, 28, 28, 64, 256, 1, 1),
+            conv_wgrad_plain(5, 14, 14, 256, 64, 1, 2), conv_wgrad_plain(2, 7, 7, 512, 512, 3, 1, torch.bfloat16)]
 
 
 def small_conv_cases():

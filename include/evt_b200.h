@@ -55,8 +55,13 @@ enum evtb_kind {
                                X must be 32-byte aligned for fp32 features.        FusedSpmm   :973 */
   EVTB_CONV_FPROP = 7,      /* NHWC implicit GEMM: operands [x (N,H,W,C), w (K,R,S,C)], result rows = N*P*Q,
                                columns = K; geometry in evtb_desc.conv         FusedConvFprop  evt_fuser.py:282 */
-  EVTB_CONV_DGRAD = 8       /* data gradient: operands [dy (N,P,Q,K), w (K,R,S,C)], result rows = N*H*W,
+  EVTB_CONV_DGRAD = 8,      /* data gradient: operands [dy (N,P,Q,K), w (K,R,S,C)], result rows = N*H*W,
                                columns = C                                     FusedConvDgrad  evt_fuser.py:365 */
+  EVTB_CONV_WGRAD = 9       /* weight gradient: operands [dy (N,P,Q,K), x (N,H,W,C)], result = the [K, R*S*C]
+                               matrix of the channels-last filter gradient; M = K, N = R*S*C, tile_n divides C,
+                               split_k cuts the N*P*Q reduction.  In the reference this leaf is a cuDNN call
+                               without epilogue (pass_decomposition.py:92-107); here it is an implicit GEMM on
+                               the same kernels as the other two passes. */
 };
 
 enum evtb_dtype { EVTB_F16 = 0, EVTB_BF16 = 1, EVTB_F32 = 2 };
@@ -112,8 +117,8 @@ typedef struct evtb_desc {
                              (there the step is a separate kernel, evt_fuser.py:700-826). */
   int32_t n_tma_stores;   /* GEMM / BGEMM: results written through TMA (0..4) */
   evtb_tma_store tma_stores[4];
-  evtb_conv conv;         /* CONV_FPROP / CONV_DGRAD only.  Channel counts must be multiples of 64 (the reduction
-                             runs in 64-channel blocks through TMA boxes), dilation 1 for the data gradient. */
+  evtb_conv conv;         /* CONV_* only.  Channel counts must be multiples of 64 (operands move in 64-channel
+                             blocks through TMA boxes), dilation 1 for the data gradient. */
 } evtb_desc;
 
 /* Per-launch scalars (all optional; pass NULL for none). */

@@ -220,10 +220,10 @@ def leaf_inputs(name):
         case = P.spmm_case(SPMM["n"], SPMM["edges"], SPMM["F"], "plain")
         crow, col, val, x = case.inputs
         return dict(crow=crow, col=col, val=val, x=x)
-    if name in ("conv_fprop", "conv_dgrad"):
+    if name in ("conv_fprop", "conv_dgrad", "conv_wgrad"):
         x, w, dy = _conv_tensors(CONV, LEAF_SEED + 10)
         return dict(x=x, w=w, dy=dy, geo=CONV)
-    if name in ("conv_fprop_s2", "conv_dgrad_s2"):
+    if name in ("conv_fprop_s2", "conv_dgrad_s2", "conv_wgrad_s2"):
         x, w, dy = _conv_tensors(CONV_S2, LEAF_SEED + 20)
         return dict(x=x, w=w, dy=dy, geo=CONV_S2)
     x, dy, gamma, beta = _bn_tensors(LEAF_SEED + 30)
@@ -253,6 +253,10 @@ def leaf_call(fns, name, t, upcast=True):
         g = t["geo"]
         return (fns.convolution_backward_data_channel_last(u(t["dy"]), u(t["x"]), u(t["w"]), g["stride"], g["padding"],
                                                            g["dilation"], False, [0, 0], 1),)
+    if name.startswith("conv_wgrad"):
+        g = t["geo"]
+        return (fns.convolution_backward_weight_channel_last(u(t["dy"]), u(t["x"]), u(t["w"]), g["stride"], g["padding"],
+                                                             g["dilation"], False, [0, 0], 1).contiguous(),)
     # batch norm: the four leaves chained as the decomposed graph chains them
     x, dy, gamma, beta = t["x"], t["dy"], t["gamma"], t["beta"]
     mean, mean_x2 = fns.batch_norm_stat(x, t["rf"])
@@ -262,7 +266,7 @@ def leaf_call(fns, name, t, upcast=True):
     return (mean, mean_x2, y, saved_mean, saved_rstd, sum_dy, sum_dy_xhat, dx, dgamma, dbeta)
 
 
-LEAVES = ["spmm", "conv_fprop", "conv_dgrad", "conv_fprop_s2", "conv_dgrad_s2", "batch_norm"]
+LEAVES = ["spmm", "conv_fprop", "conv_dgrad", "conv_fprop_s2", "conv_dgrad_s2", "conv_wgrad", "conv_wgrad_s2", "batch_norm"]
 
 # ---------------------------------------------------------------------------------------------
 # Dropout (unittest/evt_fuser/dropout.py:33-75): the reference module calls aten.native_dropout,

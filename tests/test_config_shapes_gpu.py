@@ -41,6 +41,8 @@ def test_vit_row_kernel_shapes(case, cuda_device):
 @pytest.mark.parametrize("case", [
     P.conv_fprop_bn_stat(128, 56, 56, 64, 64, 3, 1),          # conv2_x 3x3 at the configuration's batch
     P.conv_dgrad_strided(128, 28, 28, 128, 256, 3, 2),        # unittest/evt_fuser/conv.py:80-97 at full size
+    P.conv_wgrad_plain(128, 56, 56, 64, 64, 3, 1),            # weight gradient of conv2_x 3x3: 401,408 positions reduced
+    P.conv_wgrad_plain(128, 14, 14, 256, 256, 3, 1),          # conv4_x 3x3
 ], ids=lambda c: c.name)
 def test_resnet_conv_full_batch(case, cuda_device):
     run_gemm_case(case, cuda_device)

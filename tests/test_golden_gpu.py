@@ -62,15 +62,18 @@ def test_fused_spmm_matches_the_reference_leaf(cuda_device):
 
 
 @pytest.mark.parametrize("leaf,geo", [("conv_fprop", G.CONV), ("conv_fprop_s2", G.CONV_S2), ("conv_dgrad", G.CONV),
-                                      ("conv_dgrad_s2", G.CONV_S2)])
+                                      ("conv_dgrad_s2", G.CONV_S2), ("conv_wgrad", G.CONV), ("conv_wgrad_s2", G.CONV_S2)])
 def test_fused_convolutions_match_the_reference_leaves(leaf, geo, cuda_device):
-    """pass_decomposition.py:66-90 (channels-last forward and data-gradient leaves) through the
-    implicit-GEMM kernels, half-precision storage."""
+    """pass_decomposition.py:66-107 (channels-last forward, data-gradient and weight-gradient leaves)
+    through the implicit-GEMM kernels, half-precision storage."""
     import partitions as P
     t = G.leaf_inputs(leaf)
     if leaf.startswith("conv_fprop"):
         case = P.conv_fprop_plain(geo["N"], geo["H"], geo["W"], geo["C"], geo["K"], geo["R"], geo["stride"][0])
         case.inputs = [t["x"], t["w"]]
+    elif leaf.startswith("conv_wgrad"):
+        case = P.conv_wgrad_plain(geo["N"], geo["H"], geo["W"], geo["C"], geo["K"], geo["R"], geo["stride"][0])
+        case.inputs = [t["dy"], t["x"], t["w"]]
     else:
         case = P.conv_dgrad_strided(geo["N"], geo["H"], geo["W"], geo["C"], geo["K"], geo["R"], geo["stride"][0])
         case.inputs = [t["dy"], t["x"], t["w"]]
