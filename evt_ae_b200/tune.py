@@ -107,6 +107,24 @@ def spmm_candidates(op) -> List:
     return out
 
 
+def wgrad_candidates(op) -> List:
+    """channel-tile width x number of cuts of the N*P*Q reduction around the closed-form choice"""
+    import copy
+    base = op.tile
+    out = [base]
+    for bn in (64, 128, 256):
+        if op.geom["C"] % bn:
+            continue
+        tiles = ((op.geom["K"] + 127) // 128) * (op.geom["R"] * op.geom["S"] * op.geom["C"] // bn)
+        boxes = max(1, op.geom["N"] * op.geom["P"] * op.geom["Q"] // 64)
+        full = max(1, min(148 // max(tiles, 1), boxes // 8, 64))
+        for split in sorted({max(1, full // 2), full, min(64, full * 2)}):
+            c = GemmTileConfig(bn=bn, stages=6, epi_warps=8, split_k=split)
+            if all((c.bn, c.split_k) != (o.bn, o.split_k) for o in out):
+                out.append(c)
+    return out
+
+
 def node_candidates(op):
     """(keyword of fuse_module, candidate list, fields stored in the table) for any fused node."""
     from . import fused_ops as F
@@ -116,6 +134,8 @@ def node_candidates(op):
         return "row_config", row_candidates(op), ("tpr", "vpt", "threads")
     if isinstance(op, F._FusedConvBase):
         return "conv_tile", conv_candidates(op), ("bn", "stages", "epi_warps")
+    if isinstance(op, F.FusedConvWgrad):
+        return "tile", wgrad_candidates(op), ("bn", "stages", "epi_warps", "split_k")
     if isinstance(op, F.FusedSpmm):
         return "spmm_config", spmm_candidates(op), ("t_long", "task_len", "u_short", "u_long", "min_ctas")
     raise TypeError(type(op))
@@ -153,6 +173,10 @@ def workload_specs(name: str) -> Dict[str, Tuple[torch.nn.Module, list]]:
             out[f"fprop_{h}_{c}_{k}_{r}"] = (case.module, [torch.empty(t.shape, dtype=t.dtype, device="meta") for t in case.inputs])
         case = P.conv_dgrad_strided(128, 28, 28, 128, 256, 3, 2)
         out["dgrad_28_128_256_s2"] = (case.module, [torch.empty(t.shape, dtype=t.dtype, device="meta") for t in case.inputs])
+        for (h, c, k, r, s) in [(56, 64, 64, 3, 1), (56, 64, 256, 1, 1), (28, 128, 128, 3, 1), (14, 256, 256, 3, 1), (7, 512, 512, 3, 1),
+                                (28, 128, 256, 3, 2)]:
+            case = P.conv_wgrad_plain(128, h, h, c, k, r, s)
+            out[f"wgrad_{h}_{c}_{k}_{r}_s{s}"] = (case.module, [torch.empty(t.shape, dtype=t.dtype, device="meta") for t in case.inputs])
         return out
     if name == "gcn":
         from .workloads import cases as P
