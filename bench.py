@@ -386,6 +386,119 @@ class GcnWorkload:
         return gcn_ref.loss_and_grads(self.params, self.crow, self.col, self.dinv, self.x, self.labels)
 
 
+class VitWorkload:
+    """BASELINE configuration 3: ViT-Base/16 (12 layers, hidden 768, 12 heads, MLP 3072), 224 x 224
+    images (196 patches + class token = 197 tokens, padded to 200 masked-token rows for 16-byte row
+    pitches), batch 128, bf16, one forward + backward step, 1000 random labels, random init.
+    Patch embedding, encoder and its backward run on fused nodes inside one CUDA graph; patch
+    extraction, the head on the 128 class-token rows and the loss are eager PyTorch."""
+    name = "vit_base16_train_step_b128_224px_bf16"
+    metric = "ViT-Base/16 train-step samples/s per B200"
+    unit = "samples/s"
+    dtype = "bf16"
+    cpu_sample = ("2 encoder layers + embedding + head of the same model, batch 8, fp32 eager PyTorch forward + "
+                  "backward; samples/s scaled by (2-layer FLOPs)/(12-layer FLOPs)")
+    config_notes = ("197 tokens padded to 200 rows, padded keys masked (results equal the unpadded model's); "
+                    "no optimizer update; head (128 x 1000 x 768) and loss in eager PyTorch")
+
+    def __init__(self, B=128):
+        from evt_ae_b200.workloads import vit as wv
+        self.wv, self.cfg, self.B = wv, wv.VIT_BASE_16, B
+
+    def setup(self, device):
+        import torch.distributed as dist
+        from evt_ae_b200 import runtime
+        wv, cfg, B, dt = self.wv, self.cfg, self.B, torch.bfloat16
+        self.device = device
+        self.step = wv.VitStep(cfg, B, dtype=dt)
+        self.p = {k: v.to(device) for k, v in wv.init_params(cfg, dtype=dt).items()}
+        images, labels = wv.synthetic_batch(cfg, B)
+        self.host = [images.to(dt).pin_memory(), labels.pin_memory()]
+        self.s_images, self.s_labels = self.host[0].to(device), self.host[1].to(device)
+        self.flops = self.step.gemm_flops
+
+        def whole():
+            tok, pm = self.step.embed_tokens(self.p, self.s_images)
+            loss, grads, dtok = self.step.step(self.p, tok, self.s_labels)
+            grads.update(self.step.embed_backward(dtok, pm))
+            return loss, grads
+        side = torch.cuda.Stream()
+        side.wait_stream(torch.cuda.current_stream())
+        with torch.cuda.stream(side):
+            for _ in range(2):
+                whole()
+        torch.cuda.current_stream().wait_stream(side)
+        torch.cuda.synchronize()
+        self.step.check_status()
+        before = runtime.KERNELS_ENQUEUED
+        self.graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(self.graph, capture_error_mode="thread_local"):
+            self.s_loss, self.s_grads = whole()
+        self.launches_per_step = runtime.KERNELS_ENQUEUED - before
+        self.host_loss = torch.zeros((), dtype=torch.float32).pin_memory()
+        self.reducer = None
+        if dist.is_initialized() and dist.get_world_size() > 1:
+            from evt_ae_b200.dp import GradAllReducer
+            self.reducer = GradAllReducer(self.s_grads)
+
+    @property
+    def bytes_reduced_per_step(self):
+        return self.reducer.bytes_per_step if self.reducer is not None else 0
+
+    def _run(self):
+        self.graph.replay()
+        if self.reducer is not None:
+            self.reducer.allreduce(self.s_grads)
+        return self.s_loss
+
+    def step_device(self):
+        return self._run()
+
+    def step_e2e(self):
+        self.s_images.copy_(self.host[0], non_blocking=True)
+        self.s_labels.copy_(self.host[1], non_blocking=True)
+        loss = self._run()
+        self.host_loss.copy_(loss, non_blocking=True)
+        return loss
+
+    def h2d_bytes(self):
+        return sum(t.numel() * t.element_size() for t in self.host)
+
+    def d2h_bytes(self):
+        return 4
+
+    def value_from_ms(self, ms, n_gpus):
+        return n_gpus * self.B / (ms * 1e-3)
+
+    def check(self):
+        self.step.check_status()
+        if not torch.isfinite(self.s_loss).item():
+            raise SystemExit("non-finite loss")
+
+    def dominant_kernel(self):
+        """the MLP up-projection GEMM (25,600 x 3072 x 768, bias + erf GELU, two stores)"""
+        cfg, dt = self.cfg, torch.bfloat16
+        op = self.step.n.ops["lin_dm_gelu"]
+        T = cfg.tokens_padded * self.B
+        x = torch.randn(T, cfg.dim, device=self.device, dtype=dt)
+        byname = {"b": self.p["l0.ff1.b"], "x": x, "w": self.p["l0.ff1.w"]}
+        args = [byname[n] for n in op.input_names + [a.name for a in op.args]]
+        return "lin_dm_gelu (MLP GEMM 25600x3072x768 + bias + GELU, 2 stores)", op.flops, op.time_kernel(args, iters=20, warmup=3)
+
+    def cpu_step(self):
+        from oracle import vit_ref
+        wv = self.wv
+        if not hasattr(self, "_cpu"):
+            import dataclasses
+            cfg = dataclasses.replace(self.cfg, layers=2)
+            self._cpu = (cfg, wv.init_params(cfg, dtype=torch.float32), *wv.synthetic_batch(cfg, 8))
+        cfg, p, images, labels = self._cpu
+        return vit_ref.loss_and_grads(p, cfg, images, labels)
+
+    def cpu_value(self, seconds):
+        return 8 / seconds * (2.0 / self.cfg.layers)
+
+
 class BertLargeWorkload:
     """BASELINE configuration 1: BERT-large (24 layers, hidden 1024, 16 heads, FFN 4096,
     vocabulary 30522), batch 32 x sequence 512, bf16, one forward + backward step with the
@@ -630,7 +743,7 @@ FFN1_DRAM_TRAFFIC_BYTES = 305.7e6
 FFN1_ALGORITHMIC_BYTES = 2.0 * (16384 * 1024 + 4096 * 1024 + 2 * 16384 * 4096) + 2 * 4096
 
 WORKLOADS = {"config0": Config0Workload, "ffn1": Ffn1Workload, "conv": Conv3x3Workload, "spmm": SpmmWorkload,
-             "bert": BertLargeWorkload, "gcn": GcnWorkload}
+             "bert": BertLargeWorkload, "gcn": GcnWorkload, "vit": VitWorkload}
 
 
 def time_cpu(workload, reps=3):
@@ -744,11 +857,12 @@ def main():
             peak = peaks["tflops_burst"]
             achieved = kflops / (kernel_ms * 1e-3) / 1e12
             step_tflops = wl.flops / (ms * 1e-3) / 1e12
+            is_ffn1 = isinstance(wl, BertLargeWorkload)
             roofline = dict(bound="tensor", achieved=achieved, peak=peak, unit="TFLOP/s", frac=achieved / peak,
-                            traffic=FFN1_DRAM_TRAFFIC_BYTES,
+                            traffic=FFN1_DRAM_TRAFFIC_BYTES if is_ffn1 else None,
                             traffic_unit="bytes per launch (dram read + write), from the ncu capture summarised in "
                                          "profiles/bert_ffn1_gemm_ncu_metrics.md, not measured in this run",
-                            algorithmic_bytes=FFN1_ALGORITHMIC_BYTES, kernel=kname, kernel_ms=kernel_ms,
+                            algorithmic_bytes=FFN1_ALGORITHMIC_BYTES if is_ffn1 else None, kernel=kname, kernel_ms=kernel_ms,
                             peak_source=f"{peaks['source']} (burst: kernel timed alone)",
                             step_gemm_tflops=step_tflops, step_gemm_flops=wl.flops,
                             step_gemm_frac_of_sustained_peak=step_tflops / peaks["tflops_sustained"])
