@@ -499,6 +499,123 @@ class VitWorkload:
         return 8 / seconds * (2.0 / self.cfg.layers)
 
 
+class ResNetWorkload:
+    """BASELINE configuration 4: ResNet-50 (bottlenecks 3-4-6-3, v1.5 strides), 224 x 224 images, batch
+    128, fp16, channels-last, batch norm on batch statistics, summed cross-entropy over 1000 random
+    labels, random init; one forward + backward step.  Every 1x1 / 3x3 convolution runs as fused
+    tcgen05 nodes (forward with the batch-norm statistics in the epilogue, data gradient, weight
+    gradient); the batch-norm apply / backward elementwise passes, the 7x7 stem convolution (3 input
+    channels), max-pool, average-pool, classifier and loss are eager / library PyTorch."""
+    name = "resnet50_train_step_b128_224px_fp16_nhwc"
+    metric = "ResNet-50 train-step samples/s per B200"
+    unit = "samples/s"
+    dtype = "f16"
+    cpu_sample = ("the same network with one bottleneck per stage, batch 4, 128 x 128 images, fp32 eager PyTorch forward + "
+                  "backward; samples/s scaled by the ratio of convolution FLOPs per sample")
+    config_notes = ("fused: 52 of 53 convolutions (forward + BN statistics, data gradient, weight gradient); eager / "
+                    "library: batch-norm apply and backward elementwise passes, 7x7 stem convolution, pooling, "
+                    "classifier, loss; no optimizer update")
+
+    def __init__(self, B=128):
+        from evt_ae_b200.workloads import resnet as wr
+        self.wr, self.cfg, self.B = wr, wr.RESNET50, B
+
+    def setup(self, device):
+        import torch.distributed as dist
+        from evt_ae_b200 import runtime
+        wr, cfg, B, dt = self.wr, self.cfg, self.B, torch.float16
+        self.device = device
+        self.step = wr.ResNetStep(cfg, B, dtype=dt)
+        self.p = {k: v.to(device) for k, v in wr.init_params(cfg, dtype=dt).items()}
+        images, labels = wr.synthetic_batch(cfg, B)
+        self.host = [images.to(dt).pin_memory(), labels.pin_memory()]
+        self.s_images, self.s_labels = self.host[0].to(device), self.host[1].to(device)
+        self.flops = self.step.conv_flops
+        side = torch.cuda.Stream()
+        side.wait_stream(torch.cuda.current_stream())
+        with torch.cuda.stream(side):
+            for _ in range(2):
+                self.step.step(self.p, self.s_images, self.s_labels)
+        torch.cuda.current_stream().wait_stream(side)
+        torch.cuda.synchronize()
+        self.step.check_status()
+        before = runtime.KERNELS_ENQUEUED
+        self.graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(self.graph, capture_error_mode="thread_local"):
+            self.s_loss, self.s_grads = self.step.step(self.p, self.s_images, self.s_labels)
+        self.launches_per_step = runtime.KERNELS_ENQUEUED - before
+        self.host_loss = torch.zeros((), dtype=torch.float32).pin_memory()
+        self.reducer = None
+        if dist.is_initialized() and dist.get_world_size() > 1:
+            from evt_ae_b200.dp import GradAllReducer
+            self.reducer = GradAllReducer(self.s_grads)
+
+    @property
+    def bytes_reduced_per_step(self):
+        return self.reducer.bytes_per_step if self.reducer is not None else 0
+
+    def _run(self):
+        self.graph.replay()
+        if self.reducer is not None:
+            self.reducer.allreduce(self.s_grads)
+        return self.s_loss
+
+    def step_device(self):
+        return self._run()
+
+    def step_e2e(self):
+        self.s_images.copy_(self.host[0], non_blocking=True)
+        self.s_labels.copy_(self.host[1], non_blocking=True)
+        loss = self._run()
+        self.host_loss.copy_(loss, non_blocking=True)
+        return loss
+
+    def h2d_bytes(self):
+        return sum(t.numel() * t.element_size() for t in self.host)
+
+    def d2h_bytes(self):
+        return 4
+
+    def value_from_ms(self, ms, n_gpus):
+        return n_gpus * self.B / (ms * 1e-3)
+
+    def check(self):
+        self.step.check_status()
+        if not torch.isfinite(self.s_loss).item():
+            raise SystemExit("non-finite loss")
+
+    def dominant_kernel(self):
+        """the 3x3 convolution of the second stage (128 x 28 x 28 x 128 -> 128 channels) with the
+        batch-norm statistics in its epilogue"""
+        B, dt = self.B, torch.float16
+        geo = (B, 28, 28, 128, 128, 3, 1)
+        op = self.step.ops["fprop_" + "x".join(map(str, geo))]
+        x = torch.randn(B, 28, 28, 128, device=self.device, dtype=dt)
+        w = (torch.randn(128, 3, 3, 128, device=self.device) * 0.03).to(dt)
+        byname = {"x": x, "w": w}
+        args = [byname[n] for n in op.input_names + [a.name for a in op.args]]
+        return "conv 3x3 fprop 128x28x28x128->128 + BN statistics", op.flops, op.time_kernel(args, iters=20, warmup=3)
+
+    def _cpu_cfg(self):
+        import dataclasses
+        return dataclasses.replace(self.cfg, layers=(1, 1, 1, 1), image=128)
+
+    def cpu_step(self):
+        from oracle import resnet_ref
+        wr = self.wr
+        if not hasattr(self, "_cpu"):
+            cfg = self._cpu_cfg()
+            self._cpu = (cfg, wr.init_params(cfg, dtype=torch.float32), *wr.synthetic_batch(cfg, 4))
+        cfg, p, images, labels = self._cpu
+        return resnet_ref.loss_and_grads(p, cfg, wr._arch(cfg), images, labels)
+
+    def cpu_value(self, seconds):
+        wr = self.wr
+        small = wr.conv_flops_per_sample(self._cpu_cfg())
+        full = wr.conv_flops_per_sample(self.cfg)
+        return 4 / seconds * (small / full)
+
+
 class BertLargeWorkload:
     """BASELINE configuration 1: BERT-large (24 layers, hidden 1024, 16 heads, FFN 4096,
     vocabulary 30522), batch 32 x sequence 512, bf16, one forward + backward step with the
@@ -743,7 +860,7 @@ FFN1_DRAM_TRAFFIC_BYTES = 305.7e6
 FFN1_ALGORITHMIC_BYTES = 2.0 * (16384 * 1024 + 4096 * 1024 + 2 * 16384 * 4096) + 2 * 4096
 
 WORKLOADS = {"config0": Config0Workload, "ffn1": Ffn1Workload, "conv": Conv3x3Workload, "spmm": SpmmWorkload,
-             "bert": BertLargeWorkload, "gcn": GcnWorkload, "vit": VitWorkload}
+             "bert": BertLargeWorkload, "gcn": GcnWorkload, "vit": VitWorkload, "resnet": ResNetWorkload}
 
 
 def time_cpu(workload, reps=3):

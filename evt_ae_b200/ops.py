@@ -120,6 +120,8 @@ def batch_norm_elemt(input, weight, bias, mean_vec, mean_x2_vec, eps, K):
     if input.device.type == "meta":
         v = torch.empty((input.shape[-1],), dtype=torch.float32, device="meta")
         return torch.empty_like(input), v, v.clone()
+    if input.is_cuda and input.dtype in (torch.float16, torch.bfloat16):
+        return bn_apply(input, mean_vec, mean_x2_vec, weight, bias, eps)
     mean = mean_vec.reshape(-1).to(torch.float32)
     rstd = torch.rsqrt(mean_x2_vec.reshape(-1).to(torch.float32) - mean * mean + eps)
     y = (input.to(torch.float32) - mean) * (weight.to(torch.float32) * rstd) + bias.to(torch.float32)
@@ -133,6 +135,9 @@ def batch_norm_backward_stat(y_grad, input, saved_mean, saved_rstd, K):
     if y_grad.device.type == "meta":
         v = torch.empty((input.shape[-1],), dtype=torch.float32, device="meta")
         return v, v.clone()
+    if y_grad.is_cuda and y_grad.dtype in (torch.float16, torch.bfloat16):
+        _, sums = bn_backward_reduce(y_grad, input, saved_mean, saved_rstd)
+        return sums[0], sums[1]
     g = y_grad.to(torch.float32)
     xhat = (input.to(torch.float32) - saved_mean) * saved_rstd
     return g.sum(dim=(0, 1, 2)), (g * xhat).sum(dim=(0, 1, 2))
@@ -145,6 +150,9 @@ def batch_norm_backward_elemt(y_grad, input, saved_mean, saved_rstd, K, sum_grad
     if y_grad.device.type == "meta":
         v = torch.empty((input.shape[-1],), dtype=y_grad.dtype, device="meta")
         return torch.empty_like(y_grad), v, v.clone()
+    if y_grad.is_cuda and y_grad.dtype in (torch.float16, torch.bfloat16):
+        sums = torch.stack([sum_grad_y.reshape(-1).to(torch.float32), sum_grad_y_xhat.reshape(-1).to(torch.float32)])
+        return bn_backward_apply(y_grad, input, saved_mean, saved_rstd, gamma, sums, reduction_factor)
     g = y_grad.to(torch.float32)
     xhat = (input.to(torch.float32) - saved_mean) * saved_rstd
     mean_g = sum_grad_y.reshape(-1).to(torch.float32) * reduction_factor
@@ -194,6 +202,95 @@ def colsum(x: torch.Tensor, out_dtype: torch.dtype = None) -> torch.Tensor:
     runtime._check(lib, st, "evtb_colsum")
     runtime.KERNELS_ENQUEUED += 1
     return y
+
+
+def _bn_operands(*tensors):
+    """Activations as contiguous [rows, C] views of one half-precision CUDA dtype."""
+    first = tensors[0]
+    if not first.is_cuda or first.dtype not in (torch.float16, torch.bfloat16):
+        raise RuntimeError("the batch-norm kernels run on fp16 / bf16 CUDA tensors only; there is no CPU path")
+    out = []
+    for t in tensors:
+        if t is None:
+            out.append(None)
+            continue
+        if t.dtype != first.dtype or t.shape != first.shape:
+            raise RuntimeError("batch-norm activations must share dtype and shape")
+        out.append(t.contiguous())
+    C = first.shape[-1]
+    return out, first.numel() // C, C
+
+
+def _zeroed_f32(shape, device):
+    from . import fused_ops
+    arena = fused_ops._ACTIVE_ARENA
+    t = arena.take(shape, device) if arena is not None else None
+    return t if t is not None else torch.zeros(shape, dtype=torch.float32, device=device)
+
+
+def _f32_vec(v, C):
+    v = v.reshape(-1)
+    if v.dtype != torch.float32 or v.numel() != C:
+        v = v.to(torch.float32)
+    return v.contiguous()
+
+
+def bn_apply(y, mean_vec, mean_x2_vec, gamma, beta, eps, residual=None, relu=False):
+    """z = act((y - mean) * rstd * gamma + beta [+ residual]) on a channels-last activation, from the
+    E[y], E[y^2] vectors of the producing convolution's epilogue: the reference's batch_norm_elemt
+    leaf (pass_decomposition.py:143-157) with the following ReLU / residual addition in the same
+    pass.  Returns (z, saved_mean, saved_rstd)."""
+    (y, residual), rows, C = _bn_operands(y, residual)
+    lib = runtime.load_library()
+    z = torch.empty_like(y)
+    stats = torch.empty(2, C, dtype=torch.float32, device=y.device)
+    mean_vec, mean_x2_vec = _f32_vec(mean_vec, C), _f32_vec(mean_x2_vec, C)
+    gamma, beta = gamma.to(y.dtype).contiguous(), beta.to(y.dtype).contiguous()
+    st = lib.evtb_bn_apply(y.data_ptr(), _DT[y.dtype], rows, C, mean_vec.data_ptr(), mean_x2_vec.data_ptr(),
+                           gamma.data_ptr(), beta.data_ptr(), float(eps), residual.data_ptr() if residual is not None else None,
+                           1 if relu else 0, z.data_ptr(), stats[0].data_ptr(), stats[1].data_ptr(),
+                           torch.cuda.current_stream().cuda_stream)
+    runtime._check(lib, st, "evtb_bn_apply")
+    runtime.KERNELS_ENQUEUED += 1
+    return z, stats[0], stats[1]
+
+
+def bn_backward_reduce(grad, y, mean, rstd, act=None, grad2=None):
+    """g' = (grad [+ grad2]) [* (act > 0)] and the two per-channel sums of batch-norm backward,
+    sum(g') and sum(g' * x_hat): the reference's batch_norm_backward_stat leaf
+    (pass_decomposition.py:159-168) with the ReLU mask and the gradient addition in front of it
+    in the same pass.  Returns (g', sums fp32 [2, C])."""
+    (grad, y, act, grad2), rows, C = _bn_operands(grad, y, act, grad2)
+    lib = runtime.load_library()
+    changed = act is not None or grad2 is not None
+    out = torch.empty_like(grad) if changed else None
+    sums = _zeroed_f32((2, C), grad.device)
+    mean, rstd = _f32_vec(mean, C), _f32_vec(rstd, C)
+    ptr = lambda t: t.data_ptr() if t is not None else None
+    st = lib.evtb_bn_backward_reduce(grad.data_ptr(), ptr(grad2), ptr(act), y.data_ptr(), _DT[grad.dtype], rows, C,
+                                     mean.data_ptr(), rstd.data_ptr(), ptr(out), sums.data_ptr(),
+                                     torch.cuda.current_stream().cuda_stream)
+    runtime._check(lib, st, "evtb_bn_backward_reduce")
+    runtime.KERNELS_ENQUEUED += 1
+    return (out if changed else grad), sums
+
+
+def bn_backward_apply(grad, y, mean, rstd, gamma, sums, reduction_factor):
+    """dy = (grad - mean(grad) - x_hat * mean(grad * x_hat)) * gamma * rstd and dgamma, dbeta from the
+    sums: the reference's batch_norm_backward_elemt leaf (pass_decomposition.py:170-189)."""
+    (grad, y), rows, C = _bn_operands(grad, y)
+    lib = runtime.load_library()
+    dy = torch.empty_like(grad)
+    dgb = torch.empty(2, C, dtype=grad.dtype, device=grad.device)
+    mean, rstd = _f32_vec(mean, C), _f32_vec(rstd, C)
+    sums = sums.reshape(2, C).to(torch.float32).contiguous()
+    gamma = gamma.to(grad.dtype).contiguous()
+    st = lib.evtb_bn_backward_apply(grad.data_ptr(), y.data_ptr(), _DT[grad.dtype], rows, C, mean.data_ptr(), rstd.data_ptr(),
+                                    gamma.data_ptr(), sums.data_ptr(), float(reduction_factor), dy.data_ptr(),
+                                    dgb[0].data_ptr(), dgb[1].data_ptr(), torch.cuda.current_stream().cuda_stream)
+    runtime._check(lib, st, "evtb_bn_backward_apply")
+    runtime.KERNELS_ENQUEUED += 1
+    return dy, dgb[0], dgb[1]
 
 
 def sddmm(crow: torch.Tensor, col: torch.Tensor, u: torch.Tensor, v: torch.Tensor) -> torch.Tensor:

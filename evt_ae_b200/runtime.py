@@ -25,7 +25,7 @@ EXPORTED_SYMBOLS = [
     "evtb_plan_workspace_bytes", "evtb_plan_num_main_operands", "evtb_plan_grid",
     "evtb_plan_set_profile_buffer", "evtb_launch",
     "evtb_launch_ex", "evtb_colsum_workspace_bytes", "evtb_colsum", "evtb_colsum_accumulate", "evtb_colsum_static_max_cols",
-    "evtb_colsum_static", "evtb_sddmm", "evtb_csr_build_workspace_bytes", "evtb_csr_build",
+    "evtb_colsum_static", "evtb_bn_apply", "evtb_bn_backward_reduce", "evtb_bn_backward_apply", "evtb_sddmm", "evtb_csr_build_workspace_bytes", "evtb_csr_build",
 ]
 
 
@@ -103,6 +103,10 @@ def load_library() -> ctypes.CDLL:
     lib.evtb_colsum_static_max_cols.restype = ctypes.c_int
     lib.evtb_colsum_static.argtypes = [ctypes.c_void_p, ctypes.c_int32, ctypes.c_int64, ctypes.c_int64, ctypes.c_void_p,
                                        ctypes.c_int32, ctypes.c_void_p]
+    vp, i32, i64 = ctypes.c_void_p, ctypes.c_int32, ctypes.c_int64
+    lib.evtb_bn_apply.argtypes = [vp, i32, i64, i64, vp, vp, vp, vp, ctypes.c_float, vp, i32, vp, vp, vp, vp]
+    lib.evtb_bn_backward_reduce.argtypes = [vp, vp, vp, vp, i32, i64, i64, vp, vp, vp, vp, vp]
+    lib.evtb_bn_backward_apply.argtypes = [vp, vp, i32, i64, i64, vp, vp, vp, vp, ctypes.c_float, vp, vp, vp, vp]
     _lib = lib
     return lib
 

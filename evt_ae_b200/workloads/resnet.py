@@ -1,0 +1,282 @@
+"""ResNet-50 training step (forward + backward), channels-last fp16.
+
+Topology: the reference's model (python/model_zoo/resnet/resnet_modeling.py: torchvision's v1.5
+bottleneck ResNet, batch norm without running statistics, cross-entropy summed over the batch).
+What the reference's decomposition pass makes of it (pass_decomposition.py:66-189) is what runs here:
+
+  every convolution   -> fused implicit GEMM whose epilogue also emits the per-channel E[y], E[y^2]
+                         of training-mode batch norm (`batch_norm_stat`, fused as in evt_fuser.py:1272-1284)
+  batch-norm apply    -> `batch_norm_elemt` + residual addition + ReLU in one pass (ops.bn_apply; the
+                         reference hands these partitions to TorchScript, nv_fuser.py:224-244)
+  backward            -> gradient addition + ReLU mask + `batch_norm_backward_stat` in one pass
+                         (ops.bn_backward_reduce), `batch_norm_backward_elemt` in one pass
+                         (ops.bn_backward_apply), fused data-gradient and weight-gradient convolutions
+  7x7 three-channel stem, max-pool, average pool + classifier + loss
+                      -> library / eager calls: the fused kernels move operands in 64-channel blocks
+                         (the stem has 3), pooling is the leaf the reference uses (pass_decomposition.py:109-132)
+"""
+from __future__ import annotations
+
+from dataclasses import dataclass
+from typing import Dict, List, Tuple
+
+import torch
+
+from .. import ops
+from ..fused_ops import ReductionArena
+from ..fuser import fuse_module
+
+aten = torch.ops.aten
+for _name in ("convolution_forward_channel_last", "convolution_backward_data_channel_last",
+              "convolution_backward_weight_channel_last"):
+    globals()[_name] = getattr(ops, _name)
+    torch.fx.wrap(_name)
+
+
+@dataclass
+class ResNetConfig:
+    layers: Tuple[int, ...] = (3, 4, 6, 3)
+    width: int = 64
+    classes: int = 1000
+    image: int = 224
+    in_channels: int = 3
+    eps: float = 1e-5
+
+
+RESNET50 = ResNetConfig()
+
+
+def _arch(cfg: ResNetConfig):
+    """[(name, C_in, K_out, R, stride)] of every convolution after the stem, in forward order, grouped
+    per bottleneck block: (conv1 1x1, conv2 3x3 (carries the stride), conv3 1x1, optional downsample 1x1)."""
+    blocks = []
+    inp = cfg.width
+    for si, nblocks in enumerate(cfg.layers):
+        planes = cfg.width * (2 ** si)
+        for bi in range(nblocks):
+            stride = 2 if (bi == 0 and si > 0) else 1
+            pre = f"s{si}.b{bi}."
+            convs = [(pre + "conv1", inp, planes, 1, 1), (pre + "conv2", planes, planes, 3, stride),
+                     (pre + "conv3", planes, planes * 4, 1, 1)]
+            down = (pre + "down", inp, planes * 4, 1, stride) if (stride != 1 or inp != planes * 4) else None
+            blocks.append((pre, convs, down))
+            inp = planes * 4
+    return blocks
+
+
+def init_params(cfg: ResNetConfig, seed: int = 1236, dtype=torch.float16, device="cpu") -> Dict[str, torch.Tensor]:
+    """Kaiming-normal (fan-out) filters in channels-last [K, R, S, C] layout, unit gains, zero shifts."""
+    g = torch.Generator().manual_seed(seed)
+
+    def conv(k, r, c):
+        std = (2.0 / (k * r * r)) ** 0.5
+        return (torch.randn(k, r, r, c, generator=g) * std).to(dtype).to(device)
+    p = {"stem.w": conv(cfg.width, 7, cfg.in_channels), "stem.bn.g": torch.ones(cfg.width), "stem.bn.b": torch.zeros(cfg.width)}
+    for pre, convs, down in _arch(cfg):
+        for name, c, k, r, _ in convs + ([down] if down else []):
+            p[name + ".w"] = conv(k, r, c)
+            p[name + ".bn.g"], p[name + ".bn.b"] = torch.ones(k), torch.zeros(k)
+    feat = cfg.width * 8 * 4
+    p["fc.w"] = (torch.randn(cfg.classes, feat, generator=g) * feat ** -0.5)
+    p["fc.b"] = torch.zeros(cfg.classes)
+    return {k: (v.to(dtype) if v.dim() != 4 else v).to(device) for k, v in p.items()}
+
+
+def synthetic_batch(cfg: ResNetConfig, B: int, seed: int = 1236):
+    g = torch.Generator().manual_seed(seed + 1)
+    return torch.randn(B, cfg.image, cfg.image, cfg.in_channels, generator=g), torch.randint(0, cfg.classes, (B,), generator=g)
+
+
+
+def conv_flops_per_sample(cfg: ResNetConfig) -> float:
+    """Forward + data-gradient + weight-gradient FLOPs of the 1x1 / 3x3 convolutions for one image
+    (3 x 2 x P x Q x K x R x S x C each; the stem is not counted)."""
+    h = cfg.image // 4
+    total = 0.0
+    for _, convs, down in _arch(cfg):
+        hin = h
+        for _, c, k, r, s in convs:
+            h = (h + 2 * (r // 2) - r) // s + 1
+            total += 6.0 * h * h * k * r * r * c
+        if down is not None:
+            _, c, k, r, s = down
+            po = (hin + 2 * (r // 2) - r) // s + 1
+            total += 6.0 * po * po * k * r * r * c
+    return total
+
+def _meta(shape, dtype):
+    return torch.empty(tuple(shape), dtype=dtype, device="meta")
+
+
+class ResNetStep:
+    """`step(params, images_nhwc, labels)` -> (loss, grads).  All fused convolution nodes are built
+    (and their kernels compiled) at construction, keyed by geometry and shared between layers."""
+
+    def __init__(self, cfg: ResNetConfig, B: int, dtype=torch.float16):
+        self.cfg, self.B, self.dtype = cfg, B, dtype
+        self.fprop, self.dgrad, self.wgrad = {}, {}, {}
+        self.ops: Dict[str, object] = {}
+        self.arena = None
+        self._units = {}
+        h = cfg.image // 4                      # after the stride-2 stem and the stride-2 max-pool
+        self.plan: List[tuple] = []             # (prefix, [(name, geometry)...], downsample or None)
+        for pre, convs, down in _arch(cfg):
+            entries = []
+            hin = h
+            for name, c, k, r, s in convs:
+                geo = (B, h, h, c, k, r, s)
+                self._build(geo)
+                entries.append((name, geo))
+                h = (h + 2 * (r // 2) - r) // s + 1
+            dgeo = None
+            if down is not None:
+                name, c, k, r, s = down
+                dgeo = (name, (B, hin, hin, c, k, r, s))
+                self._build(dgeo[1])
+            self.plan.append((pre, entries, dgeo))
+
+    def _build(self, geo):
+        if geo in self.fprop:
+            return
+        B, H, W, C, K, R, s = geo
+        pad = R // 2
+        P = (H + 2 * pad - R) // s + 1
+        rf = 1.0 / (B * P * P)
+        dt = self.dtype
+
+        class Fprop(torch.nn.Module):            # y = conv(x, w); E[y], E[y^2] per channel in the epilogue
+            def forward(self, x, w):
+                y = convolution_forward_channel_last(x, w, [s, s], [pad, pad], [1, 1], False, [0, 0], 1)
+                d = aten.mul(y, rf)
+                return (y, aten.sum(d, [0, 1, 2], True, dtype=torch.float32),
+                        aten.sum(aten.mul(d, y), [0, 1, 2], True, dtype=torch.float32))
+
+        class Dgrad(torch.nn.Module):
+            def forward(self, dy, x, w):
+                return convolution_backward_data_channel_last(dy, x, w, [s, s], [pad, pad], [1, 1], False, [0, 0], 1)
+
+        class Wgrad(torch.nn.Module):
+            def forward(self, dy, x, w):
+                return convolution_backward_weight_channel_last(dy, x, w, [s, s], [pad, pad], [1, 1], False, [0, 0], 1)
+        x, w, dy = _meta((B, H, W, C), dt), _meta((K, R, R, C), dt), _meta((B, P, P, K), dt)
+        tag = "x".join(map(str, geo))
+        self.fprop[geo], self.ops["fprop_" + tag] = fuse_module(Fprop(), [x, w])
+        self.dgrad[geo], self.ops["dgrad_" + tag] = fuse_module(Dgrad(), [dy, x, w])
+        self.wgrad[geo], self.ops["wgrad_" + tag] = fuse_module(Wgrad(), [dy, x, w])
+
+    @property
+    def conv_flops(self) -> float:
+        """FLOPs of the fused convolutions of one step (forward, data and weight gradients)."""
+        total = 0.0
+        for _, entries, dgeo in self.plan:
+            for _, geo in entries + ([dgeo] if dgeo else []):
+                tag = "x".join(map(str, geo))
+                total += self.ops["fprop_" + tag].flops + self.ops["dgrad_" + tag].flops + self.ops["wgrad_" + tag].flops
+        return total
+
+    def check_status(self):
+        for op in self.ops.values():
+            op.check_status()
+
+    # ---------------------------------------------------------------------------------- pieces
+    def _conv_bn(self, p, name, geo, x, relu, residual=None):
+        """convolution (statistics in its epilogue) + one normalise / add / ReLU pass"""
+        y, mean, mean_x2 = self.fprop[geo](x, p[name + ".w"])
+        z, m, rstd = ops.bn_apply(y, mean, mean_x2, p[name + ".bn.g"], p[name + ".bn.b"], self.cfg.eps,
+                                  residual=residual, relu=relu)
+        return y, z, m, rstd
+
+    def _conv_bn_backward(self, p, name, geo, grads, g, x, y, m, rstd, act=None, g2=None, need_dx=True):
+        """g (+ g2): gradient w.r.t. the activation after the batch norm (and after its ReLU if `act`
+        is that activation).  Returns (masked gradient, data gradient of the convolution)."""
+        rf = 1.0 / (y.shape[0] * y.shape[1] * y.shape[2])
+        gm, sums = ops.bn_backward_reduce(g, y, m, rstd, act=act, grad2=g2)
+        dy, dg, db = ops.bn_backward_apply(gm, y, m, rstd, p[name + ".bn.g"], sums, rf)
+        grads[name + ".bn.g"], grads[name + ".bn.b"] = dg, db
+        w = p[name + ".w"]
+        grads[name + ".w"] = self.wgrad[geo](dy, x, w)
+        return gm, (self.dgrad[geo](dy, x, w) if need_dx else None)
+
+    # ---------------------------------------------------------------------------------- step
+    def step(self, p: Dict[str, torch.Tensor], images: torch.Tensor, labels: torch.Tensor):
+        cfg, dt = self.cfg, self.dtype
+        F = torch.nn.functional
+        grads: Dict[str, torch.Tensor] = {}
+        if self.arena is None or self.arena.buf.device != images.device:
+            self.arena = ReductionArena(images.device, 1 << 19)
+        self.arena.reset()
+        with self.arena:
+            return self._step(p, images, labels, grads, cfg, dt, F)
+
+    def _step(self, p, images, labels, grads, cfg, dt, F):
+        x0 = images.to(dt)
+        # stem: library convolution (3 input channels), then statistics, normalise + ReLU, max-pool
+        y0 = ops.convolution_forward_channel_last(x0, p["stem.w"], [2, 2], [3, 3], [1, 1], False, [0, 0], 1)
+        rf0 = 1.0 / (y0.shape[0] * y0.shape[1] * y0.shape[2])
+        zero, one = self._unit(cfg.width, y0.device)
+        _, moments = ops.bn_backward_reduce(y0, y0, zero, one)               # sum(y), sum(y * y) per channel
+        a0, m0, r0 = ops.bn_apply(y0, moments[0] * rf0, moments[1] * rf0, p["stem.bn.g"], p["stem.bn.b"], cfg.eps, relu=True)
+        pooled, pool_idx = aten.max_pool2d_with_indices(a0.permute(0, 3, 1, 2), [3, 3], [2, 2], [1, 1])
+        x = pooled.permute(0, 2, 3, 1).contiguous()
+        saved = []
+        for pre, entries, dgeo in self.plan:
+            xin = x
+            acts = []
+            cur = xin
+            for j, (name, geo) in enumerate(entries[:2]):
+                y, out, m, rstd = self._conv_bn(p, name, geo, cur, relu=True)
+                acts.append((cur, y, m, rstd, out))
+                cur = out
+            if dgeo is not None:
+                dy_, identity, dm_, dr_ = self._conv_bn(p, dgeo[0], dgeo[1], xin, relu=False)
+                dsave = (dy_, dm_, dr_)
+            else:
+                identity, dsave = xin, None
+            name, geo = entries[2]
+            y, x, m, rstd = self._conv_bn(p, name, geo, cur, relu=True, residual=identity)   # ReLU(BN(conv3) + identity)
+            acts.append((cur, y, m, rstd, x))
+            saved.append((xin, acts, dsave))
+        feat = x.float().mean(dim=(1, 2))                                   # average pool
+        # classifier + loss (summed over the batch, as the reference's nn.CrossEntropyLoss(reduction="sum"))
+        feat_l = feat.detach().requires_grad_(True)
+        hw = {k: p[k].detach().float().requires_grad_(True) for k in ("fc.w", "fc.b")}
+        with torch.enable_grad():
+            loss = F.cross_entropy(F.linear(feat_l, hw["fc.w"], hw["fc.b"]), labels, reduction="sum")
+            gfeat, gw, gb = torch.autograd.grad(loss, [feat_l, hw["fc.w"], hw["fc.b"]])
+        grads["fc.w"], grads["fc.b"] = gw, gb
+        hw_ = x.shape[1] * x.shape[2]
+        g = (gfeat / hw_).to(dt).view(x.shape[0], 1, 1, x.shape[3]).expand_as(x).contiguous()
+        g2 = None
+        # ---------------------------------------------------------------- backward
+        for (pre, entries, dgeo), (xin, acts, dsave) in zip(reversed(self.plan), reversed(saved)):
+            # last convolution: the pass that takes the statistics also adds the two incoming
+            # gradients and applies the mask of the ReLU after the residual addition
+            name, geo = entries[2]
+            cur, y, m, rstd, out = acts[2]
+            dsum, d = self._conv_bn_backward(p, name, geo, grads, g, cur, y, m, rstd, act=out, g2=g2)
+            for j in (1, 0):
+                name, geo = entries[j]
+                cur, y, m, rstd, out = acts[j]
+                _, d = self._conv_bn_backward(p, name, geo, grads, d, cur, y, m, rstd, act=out)
+            if dgeo is not None:
+                dy_, dm_, dr_ = dsave
+                _, d_id = self._conv_bn_backward(p, dgeo[0], dgeo[1], grads, dsum, xin, dy_, dm_, dr_)
+            else:
+                d_id = dsum
+            g, g2 = d, d_id
+        dx = g + g2
+        # max-pool, ReLU, batch norm and weight gradient of the stem (no data gradient: images)
+        da0 = aten.max_pool2d_with_indices_backward(dx.permute(0, 3, 1, 2), a0.permute(0, 3, 1, 2), [3, 3], [2, 2], [1, 1],
+                                                    [1, 1], False, pool_idx).permute(0, 2, 3, 1)
+        dz0, sums0 = ops.bn_backward_reduce(da0, y0, m0, r0, act=a0)
+        dy0, dg0, db0 = ops.bn_backward_apply(dz0, y0, m0, r0, p["stem.bn.g"], sums0, rf0)
+        grads["stem.bn.g"], grads["stem.bn.b"] = dg0, db0
+        grads["stem.w"] = ops.convolution_backward_weight_channel_last(dy0, x0, p["stem.w"], [2, 2], [3, 3], [1, 1], False,
+                                                                       [0, 0], 1)
+        return loss.detach(), grads
+
+    def _unit(self, C, device):
+        key = (C, str(device))
+        if key not in self._units:
+            self._units[key] = (torch.zeros(C, dtype=torch.float32, device=device), torch.ones(C, dtype=torch.float32, device=device))
+        return self._units[key]

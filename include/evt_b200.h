@@ -173,6 +173,33 @@ int evtb_colsum_workspace_bytes(int64_t rows, int64_t cols, size_t* bytes);
 int evtb_colsum(const void* x, int32_t in_dtype, int64_t rows, int64_t cols, void* y, int32_t out_dtype,
                 void* workspace, size_t workspace_bytes, evtb_stream stream);
 
+/* Training-mode batch norm on a channels-last activation seen as [rows, channels] (rows = N*H*W,
+ * fp16 or bf16, contiguous, 16-byte aligned, channels % 8 == 0, channels <= 4096): the three leaves the
+ * reference's decomposition leaves outside a convolution epilogue -- batch_norm_elemt,
+ * batch_norm_backward_stat, batch_norm_backward_elemt
+ * (python/gtl/compiler/passes/pass_decomposition.py:143-189) -- one pass over the activation each.
+ * Per-channel statistics are fp32 vectors; gamma / beta / dgamma / dbeta have the activation's type.
+ * Nothing is allocated; enqueue only.
+ *
+ * evtb_bn_apply: z = (y - mean) * rstd * gamma + beta, rstd = rsqrt(mean_sq - mean^2 + eps), from the
+ *   E[y], E[y^2] vectors a convolution epilogue produced; optionally + residual (NULL for none) and
+ *   max(., 0) (relu != 0).  saved_mean / saved_rstd (NULL to skip) receive the statistics.
+ * evtb_bn_backward_reduce: g' = grad (+ grad2 if not NULL) (zeroed where act <= 0 if act is not NULL),
+ *   written to grad_out (required when g' differs from grad, else may be NULL);
+ *   sums[c] += sum_r g'[r, c], sums[channels + c] += sum_r g'[r, c] * (y[r, c] - mean[c]) * rstd[c]
+ *   with fp32 atomics: the caller zero-fills `sums` (2 * channels floats) before the launch.
+ * evtb_bn_backward_apply: dy = (grad - sums[c] * rf - x_hat * sums[channels + c] * rf) * gamma * rstd;
+ *   dgamma = sums[channels + c], dbeta = sums[c] (NULL to skip). */
+int evtb_bn_apply(const void* y, int32_t dtype, int64_t rows, int64_t channels, const float* mean, const float* mean_sq,
+                  const void* gamma, const void* beta, float eps, const void* residual, int32_t relu, void* z,
+                  float* saved_mean, float* saved_rstd, evtb_stream stream);
+int evtb_bn_backward_reduce(const void* grad, const void* grad2, const void* act, const void* y, int32_t dtype,
+                            int64_t rows, int64_t channels, const float* mean, const float* rstd, void* grad_out,
+                            float* sums, evtb_stream stream);
+int evtb_bn_backward_apply(const void* grad, const void* y, int32_t dtype, int64_t rows, int64_t channels,
+                           const float* mean, const float* rstd, const void* gamma, const float* sums,
+                           float reduction_factor, void* dy, void* dgamma, void* dbeta, evtb_stream stream);
+
 /* SDDMM on a CSR pattern (int32 indices, fp32 features, F % 4 == 0):
  * out[p] = dot(U[i, :], V[col[p], :]) for every stored (i, col[p]).  Edge gradients of a GCN
  * layer; the reference has no SDDMM (its GCN backward is a second SpMM,

@@ -1,0 +1,47 @@
+"""The ResNet training step (fused forward / data-gradient / weight-gradient convolutions with
+batch-norm statistics in the epilogue, one-pass batch-norm apply and backward kernels, library stem
+and pooling) on the GPU against fp32 autograd on the CPU, at reduced depth and image size.
+
+Batch norm over a few hundred samples followed by ReLU makes the gradients of this network sensitive
+to rounding: plain fp16 autograd of the same model differs from the fp32 result by 5-17 % per tensor
+(relative Frobenius norm) at these sizes.  The test therefore measures that difference in the same run
+(the oracle executed in fp16 on the GPU) and requires the fused step to be no further from the fp32
+gradients than 1.3 x that + 1 %; the loss must agree to 2e-3 relative and the classifier gradients, which
+sit before the sensitive part of the backward pass, to 1e-2."""
+import pytest
+import torch
+
+from evt_ae_b200.workloads import resnet as wr
+from oracle import resnet_ref
+
+pytestmark = pytest.mark.gpu
+
+
+def _rel(a, r):
+    return ((a - r).norm() / r.norm()).item()
+
+
+@pytest.mark.parametrize("layers,image,B", [((1, 1, 1, 1), 64, 8), ((2, 1, 1, 1), 96, 4)])
+def test_resnet_step_gradients(layers, image, B, cuda_device):
+    cfg = wr.ResNetConfig(layers=layers, image=image, classes=10)
+    dt, dev = torch.float16, cuda_device
+    arch = wr._arch(cfg)
+    params = {k: v.to(dt).to(torch.float32) for k, v in wr.init_params(cfg, seed=7, dtype=torch.float32).items()}
+    images, labels = wr.synthetic_batch(cfg, B, seed=7)
+    images = images.to(dt).to(torch.float32)
+    ref_loss, ref_grads = resnet_ref.loss_and_grads(params, cfg, arch, images, labels)
+    half_loss, half_grads = resnet_ref.loss_and_grads(params, cfg, arch, images, labels, dtype=dt, device=dev)
+    step = wr.ResNetStep(cfg, B, dtype=dt)
+    p = {k: v.to(dt).to(dev) for k, v in params.items()}
+    loss, grads = step.step(p, images.to(dev), labels.to(dev))
+    torch.cuda.synchronize()
+    step.check_status()
+    assert abs(loss.item() - ref_loss.item()) <= 2e-3 * abs(ref_loss.item()), (loss.item(), ref_loss.item())
+    assert set(grads) == set(ref_grads)
+    for k, r in ref_grads.items():
+        g = grads[k].float().cpu().reshape(r.shape)
+        assert torch.isfinite(g).all(), k
+        ours, half = _rel(g, r), _rel(half_grads[k].reshape(r.shape), r)
+        assert ours <= 1.3 * half + 1e-2, (k, ours, half)
+        if k.startswith("fc."):
+            assert ours <= 1e-2, (k, ours)
