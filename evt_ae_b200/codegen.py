@@ -97,7 +97,8 @@ class EpilogueSource:
 
 class EpilogueGenerator:
     def __init__(self, ir: EpilogueIR, struct_name: str = "Epi", row_tile: int = 128, col_group: int = 32,
-                 staged: bool = False, max_stage_tiles: int = 8, tma_store: bool = False):
+                 staged: bool = False, max_stage_tiles: int = 8, tma_store: bool = False,
+                 defer_col_reductions: bool = False):
         """row_tile: rows a CTA covers per step (a row predicate is needed unless M is a
         multiple of it; 0 = always predicate); col_group: columns the kernel guarantees to be
         in range whenever it calls visit8 with an in-range first column."""
@@ -112,6 +113,12 @@ class EpilogueGenerator:
         self.body_post: List[str] = []    # per 8-group, after the loop (vector stores)
         self.chunk_end: List[str] = []
         self.end: List[str] = []
+        self.methods: List[str] = []      # extra member functions (flush of deferred reductions)
+        # [N]-vector reductions of a tensor-core kernel (32-column chunks, per-warp staging memory) may
+        # collect a column strip's partial results before they go to global memory
+        self.defer_col_reductions = defer_col_reductions and col_group == 32
+        self.deferred = 0
+        self.finish: List[str] = []       # once per warp after its last tile
         self.uses_rand = False
         # predicates known at generation time disappear from the code
         self.staged = staged
@@ -577,11 +584,49 @@ class EpilogueGenerator:
             self.body_elem.append(
                 f"rr_{nm}[G * 8 + j] = ({self.ROW_OK} && {self._col_ok('n + j')}) ? ({src}) : {ident};")
             lpart = [_fexpr("(long long)c.l", f, self.ir.L) for f in t.factors if f.axis == "l"]
-            off = _sum(lpart + [self._col_offset(t, "n + c.lane")])
-            self.chunk_end.append("{")
-            self.chunk_end.append(f"  const float r = warp_transpose_reduce32<{opc}>(rr_{nm}, c.lane);")
-            self.chunk_end.append(f"  if ({self._col_ok('n + c.lane')} && EVTB_CHK(c, {off}, 1, {t.numel}LL, {slot})) {red}({base} + ({off}), r);")
-            self.chunk_end.append("}")
+            if lpart or not self.defer_col_reductions:
+                off = _sum(lpart + [self._col_offset(t, "n + c.lane")])
+                self.chunk_end.append("{")
+                self.chunk_end.append(f"  const float r = warp_transpose_reduce32<{opc}>(rr_{nm}, c.lane);")
+                self.chunk_end.append(f"  if ({self._col_ok('n + c.lane')} && EVTB_CHK(c, {off}, 1, {t.numel}LL, {slot})) {red}({base} + ({off}), r);")
+                self.chunk_end.append("}")
+            else:
+                # A persistent CTA walks many tiles of one column strip in a row (row tiles run
+                # fastest in every tile order): the warp keeps the strip's partial results -- one
+                # word per lane and 32-column chunk, in its own staging memory -- and sends them to
+                # global memory when the strip changes and after its last tile: one atomic per
+                # column, warp and strip instead of one per tile.  With 3136 row tiles over 256
+                # columns (a 1x1 convolution on 128 x 56 x 56 positions) the atomics on the 512
+                # result words otherwise cost more than the convolution.
+                if self.deferred % 2 == 0:
+                    self.deferred_tile = self.stage_tiles
+                    self.stage_tiles += 1
+                part = (f"(reinterpret_cast<float*>(c.stage + {self.deferred_tile} * kStageTileBytes) + "
+                        f"{(self.deferred % 2) * 256} + c.lane)")
+                self.deferred += 1
+                self.members += [f"unsigned dr_mask_{nm} = 0u;", f"int dr_n0_{nm} = 0;"]
+                off = self._col_offset(t, "col")
+                self.methods += [
+                    f"__device__ __forceinline__ void flush_{nm}(const EpiCtx& c) {{",
+                    f"  const float* d = {part};",
+                    "#pragma unroll",
+                    "  for (int k = 0; k < 8; ++k) {",
+                    f"    const int col = dr_n0_{nm} + k * 32 + c.lane;",
+                    f"    if (((dr_mask_{nm} >> k) & 1u) && {self._col_ok('col')} && EVTB_CHK(c, {off}, 1, {t.numel}LL, {slot})) "
+                    f"{red}({base} + ({off}), d[k * 32]);",
+                    "  }",
+                    f"  dr_mask_{nm} = 0u;",
+                    "}"]
+                self.begin.append(f"if (dr_mask_{nm} != 0u && dr_n0_{nm} != c.n0) flush_{nm}(c);")
+                self.begin.append(f"dr_n0_{nm} = c.n0;")
+                self.chunk_end.append("{")
+                self.chunk_end.append(f"  const float r = warp_transpose_reduce32<{opc}>(rr_{nm}, c.lane);")
+                self.chunk_end.append("  const int k = ((n - c.n0) >> 5) & 7;")
+                self.chunk_end.append(f"  float* d = {part} + k * 32;     // a word only this lane touches")
+                self.chunk_end.append(f"  *d = ((dr_mask_{nm} >> k) & 1u) ? {opc}::apply(*d, r) : r;")
+                self.chunk_end.append(f"  dr_mask_{nm} |= 1u << k;")
+                self.chunk_end.append("}")
+                self.finish.append(f"flush_{nm}(c);")
         elif "n" in axes:
             # [M]-vector result: stays in the thread across the whole tile row
             self.members.append(f"float cr_{nm};")
@@ -597,6 +642,7 @@ class EpilogueGenerator:
         s = []
         s.append(f"struct {self.struct_name} {{")
         s.append(ind(self.members, 2))
+        s.append(ind(self.methods, 2))
         s.append("  __device__ __forceinline__ void tile_begin(const EpiCtx& c) {")
         s.append(ind(self.begin, 4))
         s.append("  }")
@@ -682,6 +728,7 @@ class EpilogueGenerator:
         s.append("  }")
         s.append("  // once per warp after its last tile: bulk stores still in flight complete before the CTA leaves")
         s.append("  __device__ __forceinline__ void finish(const EpiCtx& c) {")
+        s.append(ind(self.finish, 4))
         if self.tma_stores:
             s.append("    if (c.lane == 0) tma_store_wait_all<0>();")
             s.append("    __syncwarp();")
@@ -857,7 +904,10 @@ def conv_source(ir: EpilogueIR, dgrad: bool, dtype: torch.dtype, cfg: ConvTileCo
     """Translation unit for one fused convolution (forward or data gradient).  The epilogue is
     generated exactly as for a GEMM over the (N*P*Q, K) result matrix; rows are always
     predicated because an accumulator tile is a box of output positions, not a row range."""
-    epi = EpilogueGenerator(ir, row_tile=0, staged=True).generate()
+    # measured at the ResNet-50 shapes: holding the column sums back pays with tiles of up to 128
+    # columns (1x1 convolutions to 64 channels: 75 -> 50 us) and costs with 256-column tiles, whose
+    # epilogue is short of registers already (64 -> 256 channels: 145 -> 200 us)
+    epi = EpilogueGenerator(ir, row_tile=0, staged=True, defer_col_reductions=cfg.bn <= 128).generate()
     cfg.stage_tiles = epi.stage_tiles
     while cfg.stages > 2 and conv_smem_bytes(cfg) > 227 * 1024:
         cfg.stages -= 1

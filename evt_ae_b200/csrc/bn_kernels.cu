@@ -46,13 +46,16 @@ __global__ void __launch_bounds__(kBnThreads)
 bn_apply_kernel(const T* __restrict__ y, const float* __restrict__ mean_in, const float* __restrict__ meansq_in,
                 const T* __restrict__ gamma, const T* __restrict__ beta, float eps, const T* __restrict__ res,
                 T* __restrict__ z, float* __restrict__ saved_mean, float* __restrict__ saved_rstd, long long nvec, int kv) {
-  extern __shared__ float2 bn_ss[];      // (scale, shift) per channel
+  // (scale, shift) of channel c at [c % 8][c / 8]: the lanes of a warp work on consecutive 8-channel
+  // vectors, so for each of a vector's 8 channels they read consecutive words (no bank conflicts;
+  // channel-major order would put all lanes on two banks)
+  extern __shared__ float2 bn_ss[];
   const int C = kv * 8;
   for (int c = threadIdx.x; c < C; c += kBnThreads) {
     const float m = mean_in[c];
     const float r = rsqrtf(fmaxf(meansq_in[c] - m * m, 0.f) + eps);
     const float sc = Vec8<T>::load1(gamma + c) * r;
-    bn_ss[c] = make_float2(sc, Vec8<T>::load1(beta + c) - m * sc);
+    bn_ss[(c & 7) * kv + (c >> 3)] = make_float2(sc, Vec8<T>::load1(beta + c) - m * sc);
     if (blockIdx.x == 0) {
       if (saved_mean != nullptr) saved_mean[c] = m;
       if (saved_rstd != nullptr) saved_rstd[c] = r;
@@ -75,10 +78,10 @@ bn_apply_kernel(const T* __restrict__ y, const float* __restrict__ mean_in, cons
     for (int u = 0; u < kBnUnroll; ++u) {
       const long long i = i0 + u * stride;
       if (i >= nvec) break;
-      const float2* ss = bn_ss + ((cv0 + u * sv) % kv) * 8;
+      const float2* ss = bn_ss + (cv0 + u * sv) % kv;
 #pragma unroll
       for (int j = 0; j < 8; ++j) {
-        const float2 c = ss[j];
+        const float2 c = ss[j * kv];
         float o = fmaf(v[u][j], c.x, c.y);
         if (RES) o += r[u][j];
         if (RELU) o = fmaxf(o, 0.f);
@@ -174,16 +177,17 @@ __global__ void __launch_bounds__(kBnThreads)
 bn_backward_apply_kernel(const T* __restrict__ g, const T* __restrict__ y, const float* __restrict__ mean,
                          const float* __restrict__ rstd, const T* __restrict__ gamma, const float* __restrict__ sums,
                          float rf, T* __restrict__ dy, T* __restrict__ dgamma, T* __restrict__ dbeta, long long nvec, int kv) {
-  extern __shared__ float bn_c[];        // a[C], c1[C], c0[C]
+  extern __shared__ float bn_c[];        // a, c1, c0: three arrays of C, channel c at [c % 8][c / 8]
   const int C = kv * 8;
   for (int c = threadIdx.x; c < C; c += kBnThreads) {
     const float sg = sums[c], sgx = sums[C + c];
     const float r = rstd[c];
     const float a = Vec8<T>::load1(gamma + c) * r;
     const float c1 = -a * r * (sgx * rf);
-    bn_c[c] = a;
-    bn_c[C + c] = c1;
-    bn_c[2 * C + c] = -a * (sg * rf) - c1 * mean[c];
+    const int at = (c & 7) * kv + (c >> 3);
+    bn_c[at] = a;
+    bn_c[C + at] = c1;
+    bn_c[2 * C + at] = -a * (sg * rf) - c1 * mean[c];
     if (blockIdx.x == 0) {
       if (dgamma != nullptr) Vec8<T>::store1(dgamma + c, sgx);
       if (dbeta != nullptr) Vec8<T>::store1(dbeta + c, sg);
@@ -206,10 +210,10 @@ bn_backward_apply_kernel(const T* __restrict__ g, const T* __restrict__ y, const
     for (int u = 0; u < kBnUnroll; ++u) {
       const long long i = i0 + u * stride;
       if (i >= nvec) break;
-      const int c = ((cv0 + u * sv) % kv) * 8;
+      const float* cc = bn_c + (cv0 + u * sv) % kv;
 #pragma unroll
       for (int j = 0; j < 8; ++j)
-        vg[u][j] = fmaf(bn_c[c + j], vg[u][j], fmaf(bn_c[C + c + j], vy[u][j], bn_c[2 * C + c + j]));
+        vg[u][j] = fmaf(cc[j * kv], vg[u][j], fmaf(cc[C + j * kv], vy[u][j], cc[2 * C + j * kv]));
       Vec8<T>::store(dy + i * 8, true, vg[u]);
     }
   }

@@ -178,6 +178,15 @@ def workload_specs(name: str) -> Dict[str, Tuple[torch.nn.Module, list]]:
             case = P.conv_wgrad_plain(128, h, h, c, k, r, s)
             out[f"wgrad_{h}_{c}_{k}_{r}_s{s}"] = (case.module, [torch.empty(t.shape, dtype=t.dtype, device="meta") for t in case.inputs])
         return out
+    if name == "resnet50":
+        # every fused convolution of the ResNet-50 step at batch 128: forward with batch-norm
+        # statistics, data gradient, weight gradient of each of the 22 geometries
+        from .workloads import resnet as wr
+        out = {}
+        for geo in wr.geometries(wr.RESNET50, 128):
+            for kind, spec in wr.conv_modules(geo).items():
+                out[kind + "_" + "x".join(map(str, geo))] = spec
+        return out
     if name == "gcn":
         from .workloads import cases as P
         case = P.spmm_case(169343, 585000, 128, "sym")

@@ -108,6 +108,48 @@ def _meta(shape, dtype):
     return torch.empty(tuple(shape), dtype=dtype, device="meta")
 
 
+def conv_modules(geo, dtype=torch.float16):
+    """The three fused nodes of one convolution geometry (N, H, W, C, K, R, stride) as
+    {"fprop" | "dgrad" | "wgrad": (module, meta inputs)}: forward with the batch-norm statistics in
+    the epilogue, data gradient, weight gradient."""
+    B, H, W, C, K, R, s = geo
+    pad = R // 2
+    P = (H + 2 * pad - R) // s + 1
+    rf = 1.0 / (B * P * P)
+
+    class Fprop(torch.nn.Module):            # y = conv(x, w); E[y], E[y^2] per channel in the epilogue
+        def forward(self, x, w):
+            y = convolution_forward_channel_last(x, w, [s, s], [pad, pad], [1, 1], False, [0, 0], 1)
+            d = aten.mul(y, rf)
+            return (y, aten.sum(d, [0, 1, 2], True, dtype=torch.float32),
+                    aten.sum(aten.mul(d, y), [0, 1, 2], True, dtype=torch.float32))
+
+    class Dgrad(torch.nn.Module):
+        def forward(self, dy, x, w):
+            return convolution_backward_data_channel_last(dy, x, w, [s, s], [pad, pad], [1, 1], False, [0, 0], 1)
+
+    class Wgrad(torch.nn.Module):
+        def forward(self, dy, x, w):
+            return convolution_backward_weight_channel_last(dy, x, w, [s, s], [pad, pad], [1, 1], False, [0, 0], 1)
+    x, w, dy = _meta((B, H, W, C), dtype), _meta((K, R, R, C), dtype), _meta((B, P, P, K), dtype)
+    return {"fprop": (Fprop(), [x, w]), "dgrad": (Dgrad(), [dy, x, w]), "wgrad": (Wgrad(), [dy, x, w])}
+
+
+def geometries(cfg: ResNetConfig, B: int):
+    """Distinct (N, H, W, C, K, R, stride) of the fused convolutions of a step, in network order."""
+    h = cfg.image // 4
+    out = []
+    for _, convs, down in _arch(cfg):
+        hin = h
+        for _, c, k, r, s in convs:
+            out.append((B, h, h, c, k, r, s))
+            h = (h + 2 * (r // 2) - r) // s + 1
+        if down is not None:
+            _, c, k, r, s = down
+            out.append((B, hin, hin, c, k, r, s))
+    return list(dict.fromkeys(out))
+
+
 class ResNetStep:
     """`step(params, images_nhwc, labels)` -> (loss, grads).  All fused convolution nodes are built
     (and their kernels compiled) at construction, keyed by geometry and shared between layers."""
@@ -138,31 +180,10 @@ class ResNetStep:
     def _build(self, geo):
         if geo in self.fprop:
             return
-        B, H, W, C, K, R, s = geo
-        pad = R // 2
-        P = (H + 2 * pad - R) // s + 1
-        rf = 1.0 / (B * P * P)
-        dt = self.dtype
-
-        class Fprop(torch.nn.Module):            # y = conv(x, w); E[y], E[y^2] per channel in the epilogue
-            def forward(self, x, w):
-                y = convolution_forward_channel_last(x, w, [s, s], [pad, pad], [1, 1], False, [0, 0], 1)
-                d = aten.mul(y, rf)
-                return (y, aten.sum(d, [0, 1, 2], True, dtype=torch.float32),
-                        aten.sum(aten.mul(d, y), [0, 1, 2], True, dtype=torch.float32))
-
-        class Dgrad(torch.nn.Module):
-            def forward(self, dy, x, w):
-                return convolution_backward_data_channel_last(dy, x, w, [s, s], [pad, pad], [1, 1], False, [0, 0], 1)
-
-        class Wgrad(torch.nn.Module):
-            def forward(self, dy, x, w):
-                return convolution_backward_weight_channel_last(dy, x, w, [s, s], [pad, pad], [1, 1], False, [0, 0], 1)
-        x, w, dy = _meta((B, H, W, C), dt), _meta((K, R, R, C), dt), _meta((B, P, P, K), dt)
         tag = "x".join(map(str, geo))
-        self.fprop[geo], self.ops["fprop_" + tag] = fuse_module(Fprop(), [x, w])
-        self.dgrad[geo], self.ops["dgrad_" + tag] = fuse_module(Dgrad(), [dy, x, w])
-        self.wgrad[geo], self.ops["wgrad_" + tag] = fuse_module(Wgrad(), [dy, x, w])
+        for kind, table in (("fprop", self.fprop), ("dgrad", self.dgrad), ("wgrad", self.wgrad)):
+            module, metas = conv_modules(geo, self.dtype)[kind]
+            table[geo], self.ops[kind + "_" + tag] = fuse_module(module, metas)
 
     @property
     def conv_flops(self) -> float:
