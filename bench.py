@@ -502,19 +502,20 @@ class VitWorkload:
 class ResNetWorkload:
     """BASELINE configuration 4: ResNet-50 (bottlenecks 3-4-6-3, v1.5 strides), 224 x 224 images, batch
     128, fp16, channels-last, batch norm on batch statistics, summed cross-entropy over 1000 random
-    labels, random init; one forward + backward step.  Every 1x1 / 3x3 convolution runs as fused
-    tcgen05 nodes (forward with the batch-norm statistics in the epilogue, data gradient, weight
-    gradient); the batch-norm apply / backward elementwise passes, the 7x7 stem convolution (3 input
-    channels), max-pool, average-pool, classifier and loss are eager / library PyTorch."""
+    labels, random init; one forward + backward step.  Every convolution runs as fused tcgen05 nodes
+    (forward with the batch-norm statistics in the epilogue -- the 7x7 stem on a window view of the
+    image --, data gradient, weight gradient), batch-norm apply / backward passes are one-pass kernels
+    of this library; the stem's weight gradient, max-pool, average-pool, classifier and loss are
+    library / eager PyTorch."""
     name = "resnet50_train_step_b128_224px_fp16_nhwc"
     metric = "ResNet-50 train-step samples/s per B200"
     unit = "samples/s"
     dtype = "f16"
     cpu_sample = ("the same network with one bottleneck per stage, batch 4, 128 x 128 images, fp32 eager PyTorch forward + "
                   "backward; samples/s scaled by the ratio of convolution FLOPs per sample")
-    config_notes = ("fused: 52 of 53 convolutions (forward + BN statistics, data gradient, weight gradient); eager / "
-                    "library: batch-norm apply and backward elementwise passes, 7x7 stem convolution, pooling, "
-                    "classifier, loss; no optimizer update")
+    config_notes = ("own kernels: all 53 forward convolutions with BN statistics (the 7x7 stem through a 64-wide window "
+                    "view), 52 data gradients, 52 weight gradients, every batch-norm / ReLU / residual pass; library "
+                    "or eager PyTorch: stem weight gradient, max-pool, average pool, classifier, loss; no optimizer update")
 
     def __init__(self, B=128):
         from evt_ae_b200.workloads import resnet as wr

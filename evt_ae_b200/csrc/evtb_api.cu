@@ -134,16 +134,21 @@ int encode_operand_map(CUtensorMap* map, const void* base, int64_t inner, int64_
 // box is 64 channels x bq x bp x bn positions, traversed with the convolution stride.  To load
 // bq elements at stride s the box extent must be bq * s.
 int encode_activation_map(CUtensorMap* map, const void* base, int c, int w, int h, int n, int bq, int bp, int bn,
-                          int sw, int sh) {
+                          int sw, int sh, long long xs_w = 0, long long xs_h = 0, long long xs_n = 0) {
   Driver& d = driver();
+  if (xs_w == 0 && xs_h == 0 && xs_n == 0) {      // contiguous
+    xs_w = c;
+    xs_h = 1ll * c * w;
+    xs_n = 1ll * c * w * h;
+  }
   if ((reinterpret_cast<uintptr_t>(base) & 15u) != 0) {
     set_error("convolution operand base address is not 16-byte aligned");
     return EVTB_EINVAL;
   }
   cuuint64_t dims[4] = {static_cast<cuuint64_t>(c), static_cast<cuuint64_t>(w), static_cast<cuuint64_t>(h),
                         static_cast<cuuint64_t>(n)};
-  cuuint64_t strides[3] = {static_cast<cuuint64_t>(c) * 2, static_cast<cuuint64_t>(c) * w * 2,
-                           static_cast<cuuint64_t>(c) * w * h * 2};
+  cuuint64_t strides[3] = {static_cast<cuuint64_t>(xs_w) * 2, static_cast<cuuint64_t>(xs_h) * 2,
+                           static_cast<cuuint64_t>(xs_n) * 2};
   cuuint32_t box[4] = {64, static_cast<cuuint32_t>(bq * sw), static_cast<cuuint32_t>(bp * sh),
                        static_cast<cuuint32_t>(bn)};
   cuuint32_t estr[4] = {1, static_cast<cuuint32_t>(sw), static_cast<cuuint32_t>(sh), 1};
@@ -181,6 +186,16 @@ int ceil_div(int a, int b) { return (a + b - 1) / b; }
 
 constexpr long long kIntMax = 0x7fffffffLL;
 
+// x as a strided view: all three strides or none, positive multiples of 8 elements
+const char* check_x_strides(const evtb_conv& g, bool allowed) {
+  if (g.x_stride_w == 0 && g.x_stride_h == 0 && g.x_stride_n == 0) return nullptr;
+  if (!allowed) return "x strides apply to the forward convolution and the weight gradient only";
+  if (g.x_stride_w <= 0 || g.x_stride_h <= 0 || g.x_stride_n <= 0 || g.x_stride_w % 8 != 0 || g.x_stride_h % 8 != 0 ||
+      g.x_stride_n % 8 != 0)
+    return "x strides must all be given, positive and multiples of 8 elements";
+  return nullptr;
+}
+
 // Fills plan->conv: parity classes, taps, the 128-position box and the tile counts.
 int plan_convolution(const evtb_desc& d, evtb::ConvParams& cp, int* grid, int sm_count) {
   const evtb_conv& g = d.conv;
@@ -193,6 +208,10 @@ int plan_convolution(const evtb_desc& d, evtb::ConvParams& cp, int* grid, int sm
   if (g.P != (g.H + 2 * g.pad_h - g.dil_h * (g.R - 1) - 1) / g.stride_h + 1 ||
       g.Q != (g.W + 2 * g.pad_w - g.dil_w * (g.S - 1) - 1) / g.stride_w + 1) {
     set_error("convolution plan: P, Q do not match H, W, filter, padding and stride");
+    return EVTB_EINVAL;
+  }
+  if (const char* why = check_x_strides(g, !dgrad)) {
+    set_error(std::string("convolution plan: ") + why);
     return EVTB_EINVAL;
   }
   if (g.C % 64 != 0 || g.K % 64 != 0) {
@@ -352,7 +371,7 @@ struct evtb_plan {
 
 extern "C" {
 
-int evtb_version(void) { return 1; }
+int evtb_version(void) { return 2; }
 
 const char* evtb_status_string(int status) {
   switch (status) {
@@ -567,6 +586,7 @@ int evtb_plan_create(const evtb_desc* desc, evtb_plan** out) {
     else if (g.P != (g.H + 2 * g.pad_h - g.dil_h * (g.R - 1) - 1) / g.stride_h + 1 ||
              g.Q != (g.W + 2 * g.pad_w - g.dil_w * (g.S - 1) - 1) / g.stride_w + 1)
       bad = "weight gradient: P, Q do not match H, W, filter, padding and stride";
+    else if (check_x_strides(g, true) != nullptr) bad = "weight gradient: x strides must all be given, positive and multiples of 8 elements";
     else if (g.C % 64 != 0 || g.K % 8 != 0) bad = "weight gradient: C must be a multiple of 64 and K of 8";
     else if ((d.tile_n != 64 && d.tile_n != 128 && d.tile_n != 256) || g.C % d.tile_n != 0)
       bad = "weight gradient: tile_n must be 64, 128 or 256 and divide C";
@@ -786,7 +806,8 @@ int evtb_launch_ex(evtb_plan* plan, const void* const* ptrs, int n, void* worksp
     p.wg = plan->wg;
     int rc = encode_activation_map(&p.tma_a, ptrs[0], g.K, g.Q, g.P, g.N, p.wg.bq, p.wg.bp, p.wg.bn, 1, 1);
     if (rc != EVTB_OK) return rc;
-    rc = encode_activation_map(&p.tma_b, ptrs[1], g.C, g.W, g.H, g.N, p.wg.bq, p.wg.bp, p.wg.bn, g.stride_w, g.stride_h);
+    rc = encode_activation_map(&p.tma_b, ptrs[1], g.C, g.W, g.H, g.N, p.wg.bq, p.wg.bp, p.wg.bn, g.stride_w, g.stride_h,
+                               g.x_stride_w, g.x_stride_h, g.x_stride_n);
     if (rc != EVTB_OK) return rc;
     p.M = static_cast<int>(d.M);
     p.N = static_cast<int>(d.N);
@@ -826,7 +847,7 @@ int evtb_launch_ex(evtb_plan* plan, const void* const* ptrs, int n, void* worksp
     evtb::ConvParams cp = plan->conv;
     int rc = dgrad ? encode_activation_map(&cp.tma_a, ptrs[0], g.K, g.Q, g.P, g.N, cp.bq, cp.bp, cp.bn, 1, 1)
                    : encode_activation_map(&cp.tma_a, ptrs[0], g.C, g.W, g.H, g.N, cp.bq, cp.bp, cp.bn, g.stride_w,
-                                           g.stride_h);
+                                           g.stride_h, g.x_stride_w, g.x_stride_h, g.x_stride_n);
     if (rc != EVTB_OK) return rc;
     const int64_t rsc = 1ll * g.R * g.S * g.C;
     rc = encode_operand_map(&cp.tma_b, ptrs[1], rsc, g.K, 1, rsc, rsc * g.K, 64,

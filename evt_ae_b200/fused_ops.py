@@ -23,7 +23,7 @@ from . import codegen, jit, runtime, tuning
 from .codegen import GemmTileConfig
 from .ir import EpilogueIR
 from .ops import _conv_out_hw
-from .tracer import OperandSpec, PartitionTrace, _shape, _dtype
+from .tracer import OperandSpec, PartitionTrace, _shape, _dtype, _meta
 
 SM_COUNT_DEFAULT = 148
 SMEM_LIMIT = 227 * 1024
@@ -138,9 +138,27 @@ class ReductionArena:
 _ACTIVE_ARENA: Optional[ReductionArena] = None
 
 
+def _view_strides(node) -> Optional[tuple]:
+    """Strides of a convolution activation that is a strided view with unit channel stride, else None."""
+    tm = _meta(node)
+    st = tuple(int(v) for v in getattr(tm, "stride", ()) or ())
+    shape = tuple(int(v) for v in tm.shape)
+    if len(st) != 4:
+        return None
+    dense = (shape[1] * shape[2] * shape[3], shape[2] * shape[3], shape[3], 1)
+    if st == dense:
+        return None
+    if st[3] != 1 or any(v <= 0 or v % 8 for v in st[:3]):
+        raise NotImplementedError(f"activation view with strides {st}: the channel stride must be 1 and the others "
+                                  "positive multiples of 8 elements")
+    return st
+
+
 class FusedOpBase:
     """Base of all fused operators (reference: evt_fuser.py:62-280)."""
     __name__ = "evt_b200_fused_op"
+    view_operand = -1          # index (among the main operands) of an activation that may be a strided view
+    view_strides = None        # its strides when the plan was made for a view
     target = None
     mainloop_fusion_targets: list = []
 
@@ -186,9 +204,15 @@ class FusedOpBase:
     def __call__(self, *args_):
         n_epi = len(self.input_names)
         args = []
-        for a in args_:
-            if isinstance(a, torch.Tensor) and not a.is_contiguous():
-                a = a.contiguous()
+        for i, a in enumerate(args_):
+            if isinstance(a, torch.Tensor):
+                if self.view_strides is not None and i - n_epi == self.view_operand:
+                    # the plan was made for this strided view (a convolution activation)
+                    if tuple(a.stride()) != self.view_strides:
+                        raise RuntimeError(f"{self.__name__}: activation strides {tuple(a.stride())} differ from the "
+                                           f"plan's {self.view_strides}")
+                elif not a.is_contiguous():
+                    a = a.contiguous()
             args.append(a)
         if len(args) != n_epi + len(self.args):
             raise RuntimeError(f"{self.__name__} expects {n_epi + len(self.args)} arguments, got {len(args)}")
@@ -689,9 +713,11 @@ class _FusedConvBase(FusedOpBase):
         self.geom = dict(N=N, H=H, W=W, C=C, K=K, R=R, S=S, P=P, Q=Q, stride_h=a["stride"][0], stride_w=a["stride"][1],
                          pad_h=a["padding"][0], pad_w=a["padding"][1], dil_h=a["dilation"][0], dil_w=a["dilation"][1])
         nt = C if self.dgrad else K
+        if not self.dgrad:
+            self.view_operand, self.view_strides = 0, _view_strides(act)
         if C % 64 or K % 64:
             raise NotImplementedError("fused convolutions need channel counts that are multiples of 64 "
-                                      "(the 3-channel stem goes through a patch matrix and the GEMM)")
+                                      "(a few-channel stem is passed as a 64-wide window view, ops.stem_window)")
         import copy
         g = self.geom
         self.tune_key = tuning.key_for_node("conv_dgrad" if self.dgrad else "conv_fprop", self.ir,
@@ -721,6 +747,8 @@ class _FusedConvBase(FusedOpBase):
         d.entry = entry.encode()
         for k, v in self.geom.items():
             setattr(d.conv, k, int(v))
+        if self.view_strides is not None:
+            d.conv.x_stride_n, d.conv.x_stride_h, d.conv.x_stride_w = self.view_strides[:3]
         self.desc = d
         self.plan = runtime.Plan(d) if torch.cuda.is_available() else None
 
@@ -776,9 +804,10 @@ class FusedConvWgrad(FusedOpBase):
         N2, H, W, C2 = _shape(x)
         if K2 != K or C2 != C or N2 != N:
             raise ValueError("convolution operand shapes do not agree")
+        self.view_operand, self.view_strides = 1, _view_strides(x)
         if C % 64 or K % 8:
             raise NotImplementedError("the fused weight gradient needs C % 64 == 0 and K % 8 == 0 "
-                                      "(the 3-channel stem stays a library call)")
+                                      "(a few-channel stem is passed as a 64-wide window view, ops.stem_window)")
         self.geom = dict(N=N, H=H, W=W, C=C, K=K, R=R, S=S, P=P, Q=Q, stride_h=a["stride"][0], stride_w=a["stride"][1],
                          pad_h=a["padding"][0], pad_w=a["padding"][1], dil_h=a["dilation"][0], dil_w=a["dilation"][1])
         import copy
@@ -817,6 +846,8 @@ class FusedConvWgrad(FusedOpBase):
             d.tma_stores[i].slot, d.tma_stores[i].stride_row, d.tma_stores[i].stride_batch = ts.slot, ts.stride_row, ts.stride_batch
         for k, v in self.geom.items():
             setattr(d.conv, k, int(v))
+        if self.view_strides is not None:
+            d.conv.x_stride_n, d.conv.x_stride_h, d.conv.x_stride_w = self.view_strides[:3]
         self.desc = d
         self.plan = runtime.Plan(d) if torch.cuda.is_available() else None
         self._workspace = None

@@ -162,6 +162,67 @@ def batch_norm_backward_elemt(y_grad, input, saved_mean, saved_rstd, K, sum_grad
             sum_grad_y.reshape(-1).to(y_grad.dtype))
 
 
+class StemWindow:
+    """A few-channel convolution (the 7 x 7 / 2 stem of a ResNet on 3- or 4-channel images,
+    python/model_zoo/resnet/resnet_modeling.py:190) restated for kernels that move 64 channels at a
+    time: the taps of one filter row times the channels become the "channels".
+
+    The image is copied once into a zero-padded buffer [N, H + 2 pad, Wp, C'] (C' = channels rounded up
+    to a divisor of 64); an overlapping strided view [N, Hp, Q, 64] of it -- element (n, h, q, :) is the
+    64 / C' pixels starting at padded column q * stride_w -- is the activation, the filter becomes
+    [K, R, 1, 64] with the S taps of a row at their place inside the window (zero elsewhere), and the
+    convolution is R x 1 with stride (stride_h, 1) and no padding.  Results equal the original
+    convolution's; the filter gradient comes back through `unfold`.  Window starts are 16-byte
+    aligned, as the tensor-map loads of the fused kernels require."""
+
+    def __init__(self, x_shape, w_shape, stride, padding):
+        N, H, W, C = x_shape
+        K, R, S, Cw = w_shape
+        if Cw != C:
+            raise ValueError("image and filter channel counts differ")
+        Cp = next(c for c in (1, 2, 4, 8, 16, 32, 64) if c >= C)
+        sh, sw = stride
+        ph, pw = padding
+        px = 64 // Cp                                  # pixels per window
+        align = max(1, 8 // Cp)                        # window starts on 16-byte boundaries
+        if Cp == 64 or (sw * Cp) % 8:
+            raise NotImplementedError("window view: needs fewer than 64 channels and stride_w * channels % 8 == 0")
+        pad_l = -(-pw // align) * align
+        self.shift = pad_l - pw
+        if S + self.shift > px:
+            raise NotImplementedError(f"window view: {S} taps (+{self.shift}) do not fit {px} pixels of {Cp} channels")
+        self.P, self.Q = (H + 2 * ph - R) // sh + 1, (W + 2 * pw - S) // sw + 1
+        Wp = max(pad_l + W + pw, (self.Q - 1) * sw + px)
+        while (Wp * Cp) % 8:
+            Wp += 1
+        self.N, self.H, self.W, self.C, self.Cp, self.K, self.R, self.S = N, H, W, C, Cp, K, R, S
+        self.Hp, self.Wp, self.pad_t, self.pad_l = H + 2 * ph, Wp, ph, pad_l
+        self.view_shape = (N, self.Hp, self.Q, 64)
+        self.view_strides = (self.Hp * Wp * Cp, Wp * Cp, sw * Cp, 1)
+        self.stride, self.padding = [sh, 1], [0, 0]    # of the restated convolution
+        self.filter_shape = (K, R, 1, 64)
+
+    def image(self, x: torch.Tensor, dtype=None) -> torch.Tensor:
+        """the window view of x [N, H, W, C] (a new zero-padded buffer holds the data)"""
+        buf = torch.zeros(self.N, self.Hp, self.Wp, self.Cp, dtype=dtype or x.dtype, device=x.device)
+        buf[:, self.pad_t:self.pad_t + self.H, self.pad_l:self.pad_l + self.W, :self.C] = x
+        return buf.as_strided(self.view_shape, self.view_strides)
+
+    def meta_image(self, dtype) -> torch.Tensor:
+        return torch.empty(self.N * self.Hp * self.Wp * self.Cp, dtype=dtype, device="meta").as_strided(
+            self.view_shape, self.view_strides)
+
+    def filter(self, w: torch.Tensor) -> torch.Tensor:
+        out = torch.zeros(self.K, self.R, 64 // self.Cp, self.Cp, dtype=w.dtype, device=w.device)
+        out[:, :, self.shift:self.shift + self.S, :self.C] = w
+        return out.view(self.K, self.R, 1, 64)
+
+    def unfold(self, dw_window: torch.Tensor) -> torch.Tensor:
+        """filter gradient [K, R, S, C] from the gradient of the window filter [K, R, 1, 64]"""
+        g = dw_window.reshape(self.K, self.R, 64 // self.Cp, self.Cp)
+        return g[:, :, self.shift:self.shift + self.S, :self.C].contiguous()
+
+
 _DT = {torch.float16: runtime.EVTB_F16, torch.bfloat16: runtime.EVTB_BF16, torch.float32: runtime.EVTB_F32}
 _colsum_ws: Dict[Tuple[int, int, int, int], torch.Tensor] = {}
 

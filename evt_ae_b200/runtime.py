@@ -35,7 +35,8 @@ class evtb_matrix(ctypes.Structure):
 
 class evtb_conv(ctypes.Structure):
     _fields_ = [(n, ctypes.c_int32) for n in ("N", "H", "W", "C", "K", "R", "S", "P", "Q", "stride_h", "stride_w",
-                                              "pad_h", "pad_w", "dil_h", "dil_w")]
+                                              "pad_h", "pad_w", "dil_h", "dil_w")] + \
+               [(n, ctypes.c_int64) for n in ("x_stride_w", "x_stride_h", "x_stride_n")]
 
 
 class evtb_tma_store(ctypes.Structure):

@@ -704,6 +704,25 @@ def conv_dgrad_bn_backward_nchw(N=128, C=64, H=56, dtype=torch.float16):
     return Case(f"conv_dgrad_bn_backward_nchw_{N}x{C}x{H}", Mod(), [])
 
 
+def conv_stem_bn_nchw(N=128, C=4, K=64, H=224, dtype=torch.float16):
+    """7x7 / 2 stem convolution + training-mode batch norm on NCHW tensors (conv.py:33-49), restated
+    on the channels-last leaves: permute, convolution, statistics, normalise, permute back."""
+    from evt_ae_b200.ops import batch_norm_elemt, batch_norm_stat
+    P_ = (H + 6 - 7) // 2 + 1
+    rf = 1.0 / (N * P_ * P_)
+
+    class Mod(torch.nn.Module):
+        def forward(self, x, w, gamma, beta):
+            y = convolution_forward_channel_last(aten.permute(x, [0, 2, 3, 1]), aten.permute(w, [0, 2, 3, 1]),
+                                                 [2, 2], [3, 3], [1, 1], False, [0, 0], 1)
+            mean, mean_x2 = batch_norm_stat(y, rf)
+            out, m, rstd = batch_norm_elemt(y, gamma, beta, mean, mean_x2, 1e-5, K)
+            return aten.permute(out, [0, 3, 1, 2]), m, rstd
+    return Case(f"conv_stem_bn_nchw_{N}x{C}x{H}_k{K}_{str(dtype)[6:]}", Mod(),
+                [seeded((N, C, H, H), 55, 1.0, dtype), seeded((K, C, 7, 7), 56, 1.0, dtype), seeded((K,), 57, 1.0, dtype),
+                 seeded((K,), 58, 1.0, dtype)])
+
+
 def conv_dgrad_strided_nchw(N=128, C=128, K=256, H=28, dtype=torch.float16):
     class Mod(torch.nn.Module):
         def forward(self, grad_y, input, weight):

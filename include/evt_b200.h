@@ -79,6 +79,13 @@ typedef struct evtb_matrix {
 typedef struct evtb_conv {
   int32_t N, H, W, C, K, R, S, P, Q;
   int32_t stride_h, stride_w, pad_h, pad_w, dil_h, dil_w;
+  /* Forward and weight gradient only: element strides of x between neighbours in w, h and n when x is
+   * a strided view instead of a contiguous N x H x W x C tensor (channels always have stride 1); all
+   * three 0 = contiguous.  Each must be a multiple of 8 elements (16 bytes).  The strides may describe
+   * overlapping windows: a few-channel image seen as N x H x Q x 64 with x_stride_w = stride * channels
+   * turns the filter taps of one row into the 64 "channels" the kernels move at a time, which is how
+   * the 7 x 7 stem of a ResNet (python/model_zoo/resnet/resnet_modeling.py:190) runs here. */
+  int64_t x_stride_w, x_stride_h, x_stride_n;
 } evtb_conv;
 
 /* A result tensor that the generated GEMM epilogue writes with TMA bulk stores: element

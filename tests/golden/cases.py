@@ -80,6 +80,10 @@ def _conv_dgrad_bn(g):
     return [grad_y, x, w, bn_input, mean, torch.ops.aten.rsqrt(var), gamma]
 
 
+def _conv_stem(g):
+    return [g.randn((128, 4, 224, 224)), g.randn((64, 4, 7, 7)), g.randn((64,)), g.randn((64,))]
+
+
 def _pooler(g):
     w = g.randn((1024, 1024)) * 0.018
     x = g.randn((4, 1024))
@@ -145,13 +149,18 @@ CASES = {
                               lambda: P.conv_dgrad_bn_backward_nchw(128, 64, 56, f16)),
     "conv_dgrad_strided": ("conv.py", "test_conv_dgrad_strided", _plain((128, 256, 14, 14), (128, 128, 28, 28), (256, 128, 3, 3)),
                            lambda: P.conv_dgrad_strided_nchw(128, 128, 256, 28, f16)),
+    "conv_fprop_partition1": ("conv.py", "test_conv_fprop_partition1", _conv_stem, lambda: P.conv_stem_bn_nchw(128, 4, 64, 224, f16)),
 }
+
+# cases that are more than one fused node on the GPU (a convolution with statistics, then the
+# normalising pass): the GPU test chains the nodes itself instead of fusing the module as one partition
+MULTI_NODE = {"conv_fprop_partition1"}
 
 # cases whose restated module returns only the leading outputs of the reference's module (the
 # rest are results of library calls on both sides, e.g. convolution weight gradients)
 LEADING_OUTPUTS = {"conv_dgrad_partition1": 3, "conv_dgrad_strided": 1}
 # fp32 sums over 401,408 positions: the two eager evaluations add in different orders
-ORACLE_RTOL = {"conv_dgrad_partition1": 1e-4}
+ORACLE_RTOL = {"conv_dgrad_partition1": 1e-4, "conv_fprop_partition1": 1e-4}
 
 # tests that create their inputs in another order than they pass them (draw k <-> creation order)
 INPUT_ORDER = {"softmaxbackward": [1, 0], "mm_partition3": [1, 0, 2]}
@@ -166,7 +175,7 @@ _ORDER = ["mm_partition1", "mm_partition3", "mm_partition5", "mm_partition6", "m
           "softmaxbackward", "layer_norm_pattern1", "layer_norm_pattern2", "layer_norm_backward_pattern1",
           "conv_dgrad_partition1", "conv_dgrad_strided", "mm_partition2", "mm_partition4", "mm_partition9",
           "mm_partition12", "softmax_aux_load", "softmax_row_broadcast", "softmax_scalar_broadcast",
-          "softmax_column_reduce", "softmax_column_broadcast"]
+          "softmax_column_reduce", "softmax_column_broadcast", "conv_fprop_partition1"]
 assert sorted(_ORDER) == sorted(CASES)
 SEED_BASE = {name: 100000 + 100 * i for i, name in enumerate(_ORDER)}
 N_SAMPLES = 4096

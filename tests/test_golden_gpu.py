@@ -17,7 +17,10 @@ from evt_ae_b200.fuser import fuse_module
 pytestmark = pytest.mark.gpu
 
 
-@pytest.mark.parametrize("name", list(G.CASES), ids=list(G.CASES))
+SINGLE_NODE = [n for n in G.CASES if n not in G.MULTI_NODE]
+
+
+@pytest.mark.parametrize("name", SINGLE_NODE, ids=SINGLE_NODE)
 def test_cuda_path_matches_reference_modules(name, cuda_device):
     case = G.CASES[name][3]()
     inputs = [t.to(cuda_device) for t in G.golden_inputs(name)]
@@ -103,3 +106,21 @@ def test_fused_dropout_by_mask_reuse(cuda_device):
     ref = G.dropout_formula(case.inputs, keep.cpu())
     from oracle import compare
     assert compare(out.cpu(), ref.reshape(out.shape), "half")["bad_frac"] == 0.0
+
+
+def test_stem_convolution_and_batch_norm_match_the_reference_module(cuda_device):
+    """unittest/evt_fuser/conv.py:33-49 at its full shape (128 x 4 x 224 x 224 -> 64 channels, 7x7 / 2,
+    then training-mode batch norm): the fused forward convolution with the statistics in its epilogue on
+    the window view of the image, then the normalising kernel."""
+    from evt_ae_b200 import ops
+    from evt_ae_b200.workloads import resnet as wr
+    name = "conv_fprop_partition1"
+    x, w, gamma, beta = [t.to(cuda_device) for t in G.golden_inputs(name)]
+    xl, wl = x.permute(0, 2, 3, 1), w.permute(0, 2, 3, 1)
+    win = ops.StemWindow(xl.shape, wl.shape, [2, 2], [3, 3])
+    gm, fused = fuse_module(*wr.stem_modules(win, x.dtype)["fprop"])
+    y, mean, msq = gm(win.image(xl), win.filter(wl))
+    out, m, rstd = ops.bn_apply(y, mean, msq, gamma, beta, 1e-5)
+    torch.cuda.synchronize()
+    fused.check_status()
+    check_against_golden(name, [out.permute(0, 3, 1, 2), m, rstd], rtol=1e-2, atol=1e-3, full_numel=out.numel())

@@ -21,8 +21,8 @@ def _rel(a, r):
     return ((a - r).norm() / r.norm()).item()
 
 
-@pytest.mark.parametrize("layers,image,B", [((1, 1, 1, 1), 64, 8), ((2, 1, 1, 1), 96, 4)])
-def test_resnet_step_gradients(layers, image, B, cuda_device):
+@pytest.mark.parametrize("layers,image,B,stem_wgrad", [((1, 1, 1, 1), 64, 8, "fused"), ((2, 1, 1, 1), 96, 4, "library")])
+def test_resnet_step_gradients(layers, image, B, stem_wgrad, cuda_device):
     cfg = wr.ResNetConfig(layers=layers, image=image, classes=10)
     dt, dev = torch.float16, cuda_device
     arch = wr._arch(cfg)
@@ -31,7 +31,7 @@ def test_resnet_step_gradients(layers, image, B, cuda_device):
     images = images.to(dt).to(torch.float32)
     ref_loss, ref_grads = resnet_ref.loss_and_grads(params, cfg, arch, images, labels)
     half_loss, half_grads = resnet_ref.loss_and_grads(params, cfg, arch, images, labels, dtype=dt, device=dev)
-    step = wr.ResNetStep(cfg, B, dtype=dt)
+    step = wr.ResNetStep(cfg, B, dtype=dt, stem_wgrad=stem_wgrad)
     p = {k: v.to(dt).to(dev) for k, v in params.items()}
     loss, grads = step.step(p, images.to(dev), labels.to(dev))
     torch.cuda.synchronize()
