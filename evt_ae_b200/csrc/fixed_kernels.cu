@@ -70,6 +70,52 @@ colsum_accumulate_kernel(const TIn* __restrict__ x, float* __restrict__ y, int r
     if (c0 + j < cols) red_add_f32(y + c0 + j, acc[j]);
 }
 
+// The same sum for column counts that are multiples of 8: 256 threads = `ct` column threads (8 columns
+// each) x 256 / ct row lanes; the row lanes' sums meet in shared memory and the CTA sends ONE atomic
+// per column.  With one atomic per thread (the kernel above) 586 CTAs put 586 additions on each of
+// 1024 words and the launch took 57 us on 16384 x 1024 bf16 from cold caches; this form takes 12 us
+// (33.6 MB: 5 us at the measured copy rate).
+constexpr int kColsumWideThreads = 256;
+template <typename TIn>
+__global__ void __launch_bounds__(kColsumWideThreads)
+colsum_accumulate_wide_kernel(const TIn* __restrict__ x, float* __restrict__ y, int rows, int cols, int rows_per_chunk,
+                              int ct) {
+  __shared__ float part[kColsumWideThreads][9];
+  const int rl = kColsumWideThreads / ct;
+  const int lane_r = threadIdx.x / ct;
+  const int c0 = (blockIdx.x * ct + threadIdx.x % ct) * 8;
+  float acc[8];
+#pragma unroll
+  for (int j = 0; j < 8; ++j) acc[j] = 0.f;
+  const int r0 = blockIdx.y * rows_per_chunk;
+  const int r1 = min(rows, r0 + rows_per_chunk);
+  if (c0 < cols) {
+    for (int rb = r0 + lane_r; rb < r1; rb += rl * 4) {     // four independent row loads in flight per thread
+      float v[4][8];
+#pragma unroll
+      for (int u = 0; u < 4; ++u) {
+        const int r = rb + u * rl;
+        Vec8<TIn>::load(x + static_cast<long long>(r) * cols + c0, r < r1, v[u]);
+      }
+#pragma unroll
+      for (int u = 0; u < 4; ++u)
+#pragma unroll
+        for (int j = 0; j < 8; ++j) acc[j] += v[u][j];
+    }
+  }
+#pragma unroll
+  for (int j = 0; j < 8; ++j) part[threadIdx.x][j] = acc[j];
+  __syncthreads();
+  for (int t = threadIdx.x; t < ct * 8; t += kColsumWideThreads) {
+    const int cv = t >> 3, j = t & 7;
+    const int c = (blockIdx.x * ct + cv) * 8 + j;
+    if (c >= cols) continue;
+    float a = 0.f;
+    for (int l = 0; l < rl; ++l) a += part[l * ct + cv][j];
+    red_add_f32(y + c, a);
+  }
+}
+
 template <typename TIn, typename TOut>
 __global__ void __launch_bounds__(kColsumThreads)
 colsum_kernel(const TIn* __restrict__ x, TOut* __restrict__ y, int rows, int cols, int rows_per_chunk,
@@ -324,10 +370,32 @@ int evtb_colsum_accumulate(const void* x, int32_t in_dtype, int64_t rows, int64_
     return EVTB_EINVAL;
   if ((reinterpret_cast<uintptr_t>(x) & 15u) != 0) return EVTB_EINVAL;
   const int r = static_cast<int>(rows), c = static_cast<int>(cols);
-  const int col_blocks = (c + evtb::kColsumColsPerCta - 1) / evtb::kColsumColsPerCta;
-  // about four CTAs per SM in total; every CTA adds its rows' sums to y with one atomic per column
   int sms = evtb::current_device_sm_count();
   if (sms <= 0) sms = 148;
+  if (c % 8 == 0) {
+    // column threads per CTA: a power of two up to 64; about four CTAs per SM in total
+    int ct = 8;
+    while (ct < 64 && ct * 8 < c) ct *= 2;
+    const int rl = evtb::kColsumWideThreads / ct;
+    const int col_blocks = (c / 8 + ct - 1) / ct;
+    int chunks = (sms * 4 + col_blocks - 1) / col_blocks;
+    if (chunks > (r + rl - 1) / rl) chunks = (r + rl - 1) / rl;
+    if (chunks < 1) chunks = 1;
+    int rows_per_chunk = (r + chunks - 1) / chunks;
+    rows_per_chunk = (rows_per_chunk + rl - 1) / rl * rl;
+    chunks = (r + rows_per_chunk - 1) / rows_per_chunk;
+    const dim3 grid(col_blocks, chunks);
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    switch (in_dtype) {
+      case EVTB_F16: evtb::colsum_accumulate_wide_kernel<__half><<<grid, evtb::kColsumWideThreads, 0, s>>>(static_cast<const __half*>(x), y, r, c, rows_per_chunk, ct); break;
+      case EVTB_BF16: evtb::colsum_accumulate_wide_kernel<__nv_bfloat16><<<grid, evtb::kColsumWideThreads, 0, s>>>(static_cast<const __nv_bfloat16*>(x), y, r, c, rows_per_chunk, ct); break;
+      case EVTB_F32: evtb::colsum_accumulate_wide_kernel<float><<<grid, evtb::kColsumWideThreads, 0, s>>>(static_cast<const float*>(x), y, r, c, rows_per_chunk, ct); break;
+      default: return EVTB_EINVAL;
+    }
+    return cudaGetLastError() == cudaSuccess ? EVTB_OK : EVTB_ECUDA;
+  }
+  const int col_blocks = (c + evtb::kColsumColsPerCta - 1) / evtb::kColsumColsPerCta;
+  // ragged column counts: about four CTAs per SM in total, one atomic per column and thread
   int chunks = (sms * 4 + col_blocks - 1) / col_blocks;
   if (chunks > r) chunks = r;
   if (chunks < 1) chunks = 1;
