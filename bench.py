@@ -485,6 +485,24 @@ class VitWorkload:
         args = [byname[n] for n in op.input_names + [a.name for a in op.args]]
         return "lin_dm_gelu (MLP GEMM 25600x3072x768 + bias + GELU, 2 stores)", op.flops, op.time_kernel(args, iters=20, warmup=3)
 
+    def eager_gpu_ms(self, steps=5, warmup=3):
+        """The same model and batch as plain eager PyTorch bf16 autograd on this GPU (the oracle's module
+        moved to the device): the comparison the reference publishes.  A baseline, timed after the main
+        measurement; none of this library's kernels run in it."""
+        from oracle import vit_ref
+        dt, dev = torch.bfloat16, self.device
+        prepared = {k: v.detach().clone().to(dt).to(dev).requires_grad_(True) for k, v in self.p.items()}
+        images, labels = self.s_images, self.s_labels
+        for i in range(warmup + steps):
+            if i == warmup:
+                torch.cuda.synchronize()
+                e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                e0.record()
+            vit_ref.loss_and_grads(None, self.cfg, images, labels, dtype=dt, device=dev, prepared=prepared)
+        e1.record()
+        torch.cuda.synchronize()
+        return e0.elapsed_time(e1) / steps
+
     def cpu_step(self):
         from oracle import vit_ref
         wv = self.wv
@@ -596,6 +614,26 @@ class ResNetWorkload:
         byname = {"x": x, "w": w}
         args = [byname[n] for n in op.input_names + [a.name for a in op.args]]
         return "conv 3x3 fprop 128x28x28x128->128 + BN statistics", op.flops, op.time_kernel(args, iters=20, warmup=3)
+
+    def eager_gpu_ms(self, steps=5, warmup=3):
+        """The same model and batch as plain eager PyTorch fp16 autograd on this GPU, activations and
+        filters channels-last in memory, cuDNN with its benchmark mode on (the oracle's module moved to the
+        device): the comparison the reference publishes.  A baseline, timed after the main measurement;
+        none of this library's kernels run in it."""
+        from oracle import resnet_ref
+        dt, dev = torch.float16, self.device
+        prepared = {k: v.detach().clone().to(dt).to(dev).requires_grad_(True) for k, v in self.p.items()}
+        arch = self.wr._arch(self.cfg)
+        torch.backends.cudnn.benchmark = True
+        for i in range(warmup + steps):
+            if i == warmup:
+                torch.cuda.synchronize()
+                e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                e0.record()
+            resnet_ref.loss_and_grads(None, self.cfg, arch, self.s_images, self.s_labels, dtype=dt, device=dev, prepared=prepared)
+        e1.record()
+        torch.cuda.synchronize()
+        return e0.elapsed_time(e1) / steps
 
     def _cpu_cfg(self):
         import dataclasses
@@ -1017,7 +1055,7 @@ def main():
                 eager_ms = wl.eager_gpu_ms()
                 eager = dict(ms_per_step=eager_ms, value=wl.value_from_ms(eager_ms, 1), unit=wl.unit,
                              speedup_of_fused_step=eager_ms / ms,
-                             what="the same model and batch, eager PyTorch bf16 autograd on this GPU (baseline)")
+                             what=f"the same model and batch, eager PyTorch {wl.dtype} autograd on this GPU (baseline)")
             except Exception as e:   # the baseline must not take the measurement down
                 eager = dict(error=repr(e)[:200])
         notes = getattr(wl, "config_notes", None)

@@ -164,6 +164,11 @@ def workload_specs(name: str) -> Dict[str, Tuple[torch.nn.Module, list]]:
         # row-resident nodes (softmax fused into the GEMM) have one configuration and are not tuned
         return {k: v for k, v in step.n.specs.items()
                 if not (isinstance(step.n.ops[k], _FusedMatmulBase) and step.n.ops[k].tile.row_resident)}
+    if name == "vit":
+        from .workloads import vit as wv
+        step = wv.VitStep(wv.VIT_BASE_16, 128, dtype=torch.bfloat16)
+        return {k: v for k, v in step.n.specs.items()
+                if not (isinstance(step.n.ops[k], _FusedMatmulBase) and step.n.ops[k].tile.row_resident)}
     if name == "resnet_convs":
         # forward convolutions with batch-norm statistics and strided data gradients at ResNet-50 shapes, batch 128
         from .workloads import cases as P

@@ -13,12 +13,20 @@ import torch
 import torch.nn.functional as F
 
 
-def loss_and_grads(params: Dict[str, torch.Tensor], cfg, arch, images_nhwc, labels, dtype=torch.float32, device="cpu"):
+def loss_and_grads(params: Dict[str, torch.Tensor], cfg, arch, images_nhwc, labels, dtype=torch.float32, device="cpu",
+                   prepared=None):
     """`arch` = evt_ae_b200.workloads.resnet._arch(cfg).  Returns (loss, grads) with filter gradients in
     the [K, R, S, C] layout of the parameters.  `dtype` / `device` other than fp32 on the CPU give the
     same autograd model in reduced precision: the yardstick for how much of a difference to the fp32
     result is rounding that any half-precision run of this network shows."""
-    p = {k: v.detach().clone().to(dtype).to(device).requires_grad_(True) for k, v in params.items()}
+    if prepared is None:
+        # filters stored channels-last in memory (as the reference runs the model): the NCHW view below
+        # is then a channels_last tensor
+        p = {k: v.detach().clone().to(dtype).to(device).requires_grad_(True) for k, v in params.items()}
+    else:
+        p = prepared                       # the dictionary of an earlier call: no clones (bench.py's eager leg)
+        for v in p.values():
+            v.grad = None
     images_nhwc, labels = images_nhwc.to(device), labels.to(device)
 
     def conv_bn(x, name, stride, r):
@@ -40,4 +48,6 @@ def loss_and_grads(params: Dict[str, torch.Tensor], cfg, arch, images_nhwc, labe
     feat = x.mean(dim=(2, 3))
     loss = F.cross_entropy(F.linear(feat, p["fc.w"], p["fc.b"]).float(), labels, reduction="sum")
     loss.backward()
+    if prepared is not None:
+        return loss.detach(), {k: v.grad for k, v in p.items()}, p
     return loss.detach().cpu(), {k: v.grad.float().cpu() for k, v in p.items()}

@@ -21,12 +21,21 @@ def patchify(cfg, images):
     return x.reshape(cfg.patches, B, C * p * p)
 
 
-def loss_and_grads(params: Dict[str, torch.Tensor], cfg, images, labels):
-    p = {k: v.detach().clone().to(torch.float32).requires_grad_(True) for k, v in params.items()}
+def loss_and_grads(params: Dict[str, torch.Tensor], cfg, images, labels, dtype=torch.float32, device="cpu", prepared=None):
+    """`dtype` / `device` other than fp32 on the CPU give the same autograd model in reduced precision
+    (the eager-PyTorch baseline of bench.py); `prepared` reuses a parameter dictionary made by an
+    earlier call (returned as third value when given) instead of cloning the parameters again."""
+    if prepared is None:
+        p = {k: v.detach().clone().to(dtype).to(device).requires_grad_(True) for k, v in params.items()}
+    else:
+        p = prepared
+        for v in p.values():
+            v.grad = None
+    images, labels = images.to(device), labels.to(device)
     B = images.shape[0]
     D, nh = cfg.dim, cfg.heads
     d = D // nh
-    e = F.linear(patchify(cfg, images.to(torch.float32)), p["embed.w"], p["embed.b"])       # [patches, B, D]
+    e = F.linear(patchify(cfg, images.to(dtype)), p["embed.w"], p["embed.b"])       # [patches, B, D]
     x = torch.cat([(p["cls"] + p["pos"][0]).expand(1, B, D), e + p["pos"][1:].unsqueeze(1)], 0)
     S = x.shape[0]
     for i in range(cfg.layers):
@@ -41,6 +50,8 @@ def loss_and_grads(params: Dict[str, torch.Tensor], cfg, images, labels):
         n2 = F.layer_norm(x, (D,), p[pre + "ln2.g"], p[pre + "ln2.b"], cfg.eps)
         x = F.linear(F.gelu(F.linear(n2, p[pre + "ff1.w"], p[pre + "ff1.b"])), p[pre + "ff2.w"], p[pre + "ff2.b"]) + x
     z = F.linear(F.layer_norm(x[0], (D,), p["head.ln.g"], p["head.ln.b"], cfg.eps), p["head.w"], p["head.b"])
-    loss = F.cross_entropy(z, labels)
+    loss = F.cross_entropy(z.float(), labels)
     loss.backward()
+    if prepared is not None:
+        return loss.detach(), {k: v.grad for k, v in p.items()}, p
     return loss.detach(), {k: v.grad for k, v in p.items()}
