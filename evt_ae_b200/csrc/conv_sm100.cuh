@@ -102,9 +102,12 @@ __device__ __forceinline__ ConvTile conv_decode_tile(const ConvParams& p, int t,
 // canonical row of tile row `row` (0..127), or p.M when the row lies outside the output
 __device__ __forceinline__ int conv_row_to_m(const ConvParams& p, const ConvTile& t, int row) {
   const ConvClass& k = p.cls[t.cls];
-  const int qi = row % p.bq;
-  const int pi = (row / p.bq) % p.bp;
-  const int ni = row / (p.bq * p.bp);
+  // bq * bp * bn = 128: each is a power of two, so the split of a tile row is shifts and masks (this
+  // runs for every stored row of every 32-column chunk; with divisions it was most of the epilogue)
+  const int lq = 31 - __clz(p.bq), lp = 31 - __clz(p.bp);
+  const int qi = row & (p.bq - 1);
+  const int pi = (row >> lq) & (p.bp - 1);
+  const int ni = row >> (lq + lp);
   const int tq = t.tq0 + qi, tp = t.tp0 + pi, tn = t.tn0 + ni;
   if (tq >= k.tw || tp >= k.th || tn >= p.On) return p.M;
   const int oh = tp * p.o_sh + k.o_oh, ow = tq * p.o_sw + k.o_ow;

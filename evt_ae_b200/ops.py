@@ -110,6 +110,13 @@ def batch_norm_stat(input, reduction_factor):
     if input.device.type == "meta":
         v = torch.empty((input.shape[-1],), dtype=torch.float32, device="meta")
         return v, v.clone()
+    if input.is_cuda and input.dtype in (torch.float16, torch.bfloat16):
+        # one pass of the backward-sums kernel with mean 0 and rstd 1: sum(y) and sum(y * y)
+        C = input.shape[-1]
+        unit = _unit_vectors(C, input.device)
+        _, sums = bn_backward_reduce(input, input, unit[0], unit[1])
+        sums = sums * reduction_factor
+        return sums[0], sums[1]
     x = input.to(torch.float32)
     return x.mean(dim=(0, 1, 2)), (x * x).mean(dim=(0, 1, 2))
 
@@ -280,6 +287,18 @@ def _bn_operands(*tensors):
         out.append(t.contiguous())
     C = first.shape[-1]
     return out, first.numel() // C, C
+
+
+_units: Dict[Tuple[int, str], torch.Tensor] = {}
+
+
+def _unit_vectors(C, device):
+    """[zeros(C), ones(C)] in fp32 on `device`, made once"""
+    key = (C, str(device))
+    if key not in _units:
+        _units[key] = torch.stack([torch.zeros(C, dtype=torch.float32, device=device),
+                                   torch.ones(C, dtype=torch.float32, device=device)])
+    return _units[key]
 
 
 def _zeroed_f32(shape, device):

@@ -209,6 +209,46 @@ def workload_specs(name: str) -> Dict[str, Tuple[torch.nn.Module, list]]:
     raise SystemExit(f"unknown workload {name!r}")
 
 
+def tune_bn_stats(out_path: str, iters: int, min_gain: float):
+    """For every convolution geometry of the ResNet-50 step: the forward convolution with the batch-norm
+    statistics in its epilogue against the plain-store convolution followed by a statistics pass over its
+    output.  Writes {"separate": 1} entries (workloads/resnet.py:stats_key) where the second form wins."""
+    from . import ops
+    from .workloads import resnet as wr
+    dev, dt = torch.device("cuda:0"), torch.float16
+    entries = {}
+    for geo in wr.geometries(wr.RESNET50, 128):
+        mods = wr.conv_modules(geo, dt)
+        gm_f, op_f = fuse_module(*mods["fprop"])
+        gm_p, op_p = fuse_module(*mods["fprop_plain"])
+        inputs = [random_like(m, dev) for m in mods["fprop"][1]]
+        fused_us = statistics.median(op_f.time_kernel(fused_args(gm_f, op_f, inputs), iters=iters)) * 1e3
+        plain_us = statistics.median(op_p.time_kernel(fused_args(gm_p, op_p, inputs), iters=iters)) * 1e3
+        y = gm_p(*inputs)
+        rf = 1.0 / (y.shape[0] * y.shape[1] * y.shape[2])
+        g = torch.cuda.CUDAGraph()
+        ops.batch_norm_stat(y, rf)
+        torch.cuda.synchronize()
+        with torch.cuda.graph(g):
+            for _ in range(iters):
+                ops.batch_norm_stat(y, rf)
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        g.replay()
+        e0.record()
+        g.replay()
+        e1.record()
+        torch.cuda.synchronize()
+        stat_us = e0.elapsed_time(e1) / iters * 1e3
+        separate = plain_us + stat_us < min_gain * fused_us
+        if separate:
+            entries[wr.stats_key(geo, dt)] = dict(separate=1, fused_us=round(fused_us, 1), plain_us=round(plain_us, 1),
+                                                  stat_us=round(stat_us, 1))
+        print(json.dumps(dict(geometry=list(geo), fused_us=round(fused_us, 1), plain_us=round(plain_us, 1),
+                              stat_us=round(stat_us, 1), separate=int(separate))))
+        sys.stdout.flush()
+    tuning.save(entries, out_path)
+
+
 def main(argv=None):
     ap = argparse.ArgumentParser()
     ap.add_argument("--workload", default="bert")
@@ -218,6 +258,18 @@ def main(argv=None):
     ap.add_argument("--min-gain", type=float, default=0.96,
                     help="a candidate replaces the closed-form choice only below this fraction of its time")
     a = ap.parse_args(argv)
+    if a.workload == "resnet50_stats":
+        if a.compile_only:
+            from .workloads import resnet as wr
+            with jit.deferred() as d:
+                for geo in wr.geometries(wr.RESNET50, 128):
+                    mods = wr.conv_modules(geo, torch.float16)
+                    fuse_module(*mods["fprop"])
+                    fuse_module(*mods["fprop_plain"])
+            print("compiled", d.flush(), "kernel variants")
+            return
+        tune_bn_stats(a.out, a.iters, a.min_gain)
+        return
     specs = workload_specs(a.workload)
     def as_meta(ts):
         return [torch.empty(t.shape, dtype=t.dtype, device="meta") if t.device.type != "meta" else t for t in ts]

@@ -26,7 +26,7 @@ from typing import Dict, List, Tuple
 
 import torch
 
-from .. import ops
+from .. import ops, tuning
 from ..fused_ops import ReductionArena
 from ..fuser import fuse_module
 
@@ -135,8 +135,26 @@ def conv_modules(geo, dtype=torch.float16):
     class Wgrad(torch.nn.Module):
         def forward(self, dy, x, w):
             return convolution_backward_weight_channel_last(dy, x, w, [s, s], [pad, pad], [1, 1], False, [0, 0], 1)
+    class FpropPlain(torch.nn.Module):
+        def forward(self, x, w):
+            return convolution_forward_channel_last(x, w, [s, s], [pad, pad], [1, 1], False, [0, 0], 1)
     x, w, dy = _meta((B, H, W, C), dtype), _meta((K, R, R, C), dtype), _meta((B, P, P, K), dtype)
-    return {"fprop": (Fprop(), [x, w]), "dgrad": (Dgrad(), [dy, x, w]), "wgrad": (Wgrad(), [dy, x, w])}
+    return {"fprop": (Fprop(), [x, w]), "dgrad": (Dgrad(), [dy, x, w]), "wgrad": (Wgrad(), [dy, x, w]),
+            "fprop_plain": (FpropPlain(), [x, w])}
+
+
+def stats_key(geo, dtype=torch.float16) -> str:
+    """Key of the tuned table's entry that says where a convolution's batch-norm statistics are taken."""
+    return "bn_stats|" + "x".join(map(str, geo)) + "|" + str(dtype).replace("torch.", "")
+
+
+def separate_stats(geo, dtype=torch.float16) -> bool:
+    """True where the measured table says that a plain-store convolution followed by a statistics pass
+    over its output (ops.batch_norm_stat) beats the statistics in the epilogue: 1x1 convolutions from few
+    to many channels, whose fused epilogue (two column reductions per 32 x 32 chunk) costs more than
+    reading the output once more."""
+    e = tuning.lookup_config(stats_key(geo, dtype))
+    return bool(e and e.get("separate"))
 
 
 def stem_modules(win: "ops.StemWindow", dtype=torch.float16):
@@ -191,6 +209,7 @@ class ResNetStep:
         self.fprop, self.dgrad, self.wgrad = {}, {}, {}
         self.ops: Dict[str, object] = {}
         self.arena = None
+        self.split_stats = set()           # geometries whose statistics are a pass of their own
         self.win = ops.StemWindow((B, cfg.image, cfg.image, 3), (cfg.width, 7, 7, 3), [2, 2], [3, 3])
         mods = stem_modules(self.win, dtype)
         self.stem_fprop, self.ops["fprop_stem"] = fuse_module(*mods["fprop"])
@@ -216,8 +235,12 @@ class ResNetStep:
         if geo in self.fprop:
             return
         tag = "x".join(map(str, geo))
+        mods = conv_modules(geo, self.dtype)
+        if separate_stats(geo, self.dtype):
+            self.split_stats.add(geo)
+            mods["fprop"] = mods["fprop_plain"]
         for kind, table in (("fprop", self.fprop), ("dgrad", self.dgrad), ("wgrad", self.wgrad)):
-            module, metas = conv_modules(geo, self.dtype)[kind]
+            module, metas = mods[kind]
             table[geo], self.ops[kind + "_" + tag] = fuse_module(module, metas)
 
     @property
@@ -239,7 +262,11 @@ class ResNetStep:
     # ---------------------------------------------------------------------------------- pieces
     def _conv_bn(self, p, name, geo, x, relu, residual=None):
         """convolution (statistics in its epilogue) + one normalise / add / ReLU pass"""
-        y, mean, mean_x2 = self.fprop[geo](x, p[name + ".w"])
+        if geo in self.split_stats:
+            y = self.fprop[geo](x, p[name + ".w"])
+            mean, mean_x2 = ops.batch_norm_stat(y, 1.0 / (y.shape[0] * y.shape[1] * y.shape[2]))
+        else:
+            y, mean, mean_x2 = self.fprop[geo](x, p[name + ".w"])
         z, m, rstd = ops.bn_apply(y, mean, mean_x2, p[name + ".bn.g"], p[name + ".bn.b"], self.cfg.eps,
                                   residual=residual, relu=relu)
         return y, z, m, rstd
