@@ -43,8 +43,11 @@ def test_table_round_trip_and_lookup(tmp_path, monkeypatch):
 def test_shipped_table_is_well_formed_and_explicit_tile_wins(tmp_path, monkeypatch):
     shipped = json.load(open(tuning.TABLE_PATH))
     for key, e in shipped.items():
-        assert key.count("|") == 3
         kind = key.split("|")[0]
+        if kind == "bn_stats":       # where a convolution's batch-norm statistics are taken (workloads/resnet.py)
+            assert key.count("|") == 2 and e["separate"] in (0, 1) and e["plain_us"] + e["stat_us"] < e["fused_us"], key
+            continue
+        assert key.count("|") == 3
         if kind == "row":
             assert e["tpr"] in (8, 16, 32, 64, 128, 256, 512, 1024) and e["threads"] % 32 == 0 and 1 <= e["vpt"] <= 8, key
         elif kind == "spmm":
