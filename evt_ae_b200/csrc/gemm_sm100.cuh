@@ -126,6 +126,7 @@ template <int BN_, int STAGES_, bool A_MN_, bool B_MN_, bool BF16_, int EPI_WARP
 struct GemmConfig {
   static constexpr bool WGRAD = WGRAD_;      // operands are boxes of two 4-D convolution tensors (needs A_MN and B_MN)
   static_assert(!WGRAD_ || (A_MN_ && B_MN_ && BN_ % 64 == 0), "weight gradient: both operands MN-major, BN % 64 == 0");
+  static_assert(!WGRAD_ || !K_ROTATE_, "weight gradient: k-blocks run in order (the producer steps box counters)");
   static constexpr bool SPLIT_K = SPLIT_K_;
   static constexpr bool K_ROTATE = K_ROTATE_;
   // bytes of shared-memory staging tiles each epilogue warp owns (a multiple of 2048)
@@ -349,6 +350,20 @@ __device__ __forceinline__ void gemm_kernel_body(const GemmParams& p) {
         decode_tile(p, t, l, tm, tn);
         const int m0 = tm * kBM, n0 = tn * Cfg::BN;
         const int rot = Cfg::K_ROTATE ? static_cast<int>((blockIdx.x * 5u) % static_cast<unsigned>(kb1 - kb0)) : 0;
+        // weight gradient: box coordinates of the unit's first k-block and the column tile's filter tap;
+        // the loop then steps the box counters (one thread feeds the whole ring: three divisions per
+        // k-block were more than a narrow tile's MMA time)
+        int wq = 0, wp = 0, wi = 0, w_dh = 0, w_dw = 0, w_c0 = 0;
+        if constexpr (Cfg::WGRAD) {
+          const WgradGeom& g = p.wg;
+          wq = kb0 % g.boxes_w;
+          wp = (kb0 / g.boxes_w) % g.boxes_h;
+          wi = kb0 / (g.boxes_w * g.boxes_h);
+          const int tap = n0 / g.C;
+          w_c0 = n0 - tap * g.C;
+          w_dh = (tap / g.S) * g.dil_h - g.pad_h;
+          w_dw = (tap % g.S) * g.dil_w - g.pad_w;
+        }
         for (int ki = 0; ki < kb1 - kb0; ++ki, ++it) {
           const int kb = rotated_kb(ki, kb0, kb1, rot);
           const int s = it % Cfg::STAGES;
@@ -371,18 +386,21 @@ __device__ __forceinline__ void gemm_kernel_body(const GemmParams& p) {
           if constexpr (Cfg::WGRAD) {
             // k-block = box of 64 output positions; the column tile picks the filter tap
             const WgradGeom& g = p.wg;
-            const int q0 = (kb % g.boxes_w) * g.bq;
-            const int p0 = ((kb / g.boxes_w) % g.boxes_h) * g.bp;
-            const int i0 = (kb / (g.boxes_w * g.boxes_h)) * g.bn;
-            const int tap = n0 / g.C, c0 = n0 - tap * g.C;
-            const int dh = (tap / g.S) * g.dil_h - g.pad_h, dw = (tap % g.S) * g.dil_w - g.pad_w;
+            const int q0 = wq * g.bq, p0 = wp * g.bp, i0 = wi * g.bn;
 #pragma unroll
             for (int c = 0; c < kBM / 64; ++c)
               tma_load_4d_box(sa + c * (kBK * 128), &p.tma_a, &hdr->full[s], m0 + c * 64, q0, p0, i0);
 #pragma unroll
             for (int c = 0; c < Cfg::BN / 64; ++c)
-              tma_load_4d_box(sb + c * (kBK * 128), &p.tma_b, &hdr->full[s], c0 + c * 64, q0 * g.stride_w + dw,
-                              p0 * g.stride_h + dh, i0);
+              tma_load_4d_box(sb + c * (kBK * 128), &p.tma_b, &hdr->full[s], w_c0 + c * 64, q0 * g.stride_w + w_dw,
+                              p0 * g.stride_h + w_dh, i0);
+            if (++wq == g.boxes_w) {          // next box (k-blocks of a weight gradient run in order)
+              wq = 0;
+              if (++wp == g.boxes_h) {
+                wp = 0;
+                ++wi;
+              }
+            }
           } else if constexpr (!Cfg::A_MN) {
             tma_load_3d(sa, &p.tma_a, &hdr->full[s], k0, m0, l);
           } else {

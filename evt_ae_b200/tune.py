@@ -284,6 +284,9 @@ def main(argv=None):
         return
     if not torch.cuda.is_available():
         raise SystemExit("tuning needs a GPU (use --compile-only to build the candidates)")
+    # Candidate lists start with the node's current choice, which is the shipped table's entry where
+    # there is one; a candidate is written only if it beats that by the margin, so entries of the
+    # shipped table stay valid unless this run's output replaces them (merge, do not drop).
     dev = torch.device("cuda:0")
     entries = {}
     for name, (module, metas) in specs.items():
