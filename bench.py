@@ -523,7 +523,7 @@ class ResNetWorkload:
     labels, random init; one forward + backward step.  Every convolution runs as fused tcgen05 nodes
     (forward with the batch-norm statistics in the epilogue -- the 7x7 stem on a window view of the
     image --, data gradient, weight gradient), batch-norm apply / backward passes are one-pass kernels
-    of this library; the stem's weight gradient, max-pool, average-pool, classifier and loss are
+    and the max-pool of this library; the stem's weight gradient, average-pool, classifier and loss are
     library / eager PyTorch."""
     name = "resnet50_train_step_b128_224px_fp16_nhwc"
     metric = "ResNet-50 train-step samples/s per B200"
@@ -532,8 +532,8 @@ class ResNetWorkload:
     cpu_sample = ("the same network with one bottleneck per stage, batch 4, 128 x 128 images, fp32 eager PyTorch forward + "
                   "backward; samples/s scaled by the ratio of convolution FLOPs per sample")
     config_notes = ("own kernels: all 53 forward convolutions with BN statistics (the 7x7 stem through a 64-wide window "
-                    "view), 52 data gradients, 52 weight gradients, every batch-norm / ReLU / residual pass; library "
-                    "or eager PyTorch: stem weight gradient, max-pool, average pool, classifier, loss; no optimizer update")
+                    "view), 52 data gradients, 52 weight gradients, every batch-norm / ReLU / residual pass, max-pool; library "
+                    "or eager PyTorch: stem weight gradient, average pool, classifier, loss; no optimizer update")
 
     def __init__(self, B=128):
         from evt_ae_b200.workloads import resnet as wr

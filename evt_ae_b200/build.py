@@ -35,7 +35,8 @@ def build_library(force: bool = False, verbose: bool = False) -> str:
         return LIB
     cmd = [NVCC, "-shared", "-Xcompiler", "-fPIC", "-O3", "-std=c++17", "-lineinfo", *ARCH_FLAGS,
            "-I", CSRC, "-o", LIB, os.path.join(CSRC, "evtb_api.cu"), os.path.join(CSRC, "fixed_kernels.cu"),
-           os.path.join(CSRC, "bn_kernels.cu")]
+           os.path.join(CSRC, "bn_kernels.cu"),
+           os.path.join(CSRC, "pool_kernels.cu")]
     if verbose:
         cmd.insert(1, "-Xptxas=-v")
     r = subprocess.run(cmd, capture_output=True, text=True)

@@ -44,6 +44,7 @@ struct Driver {
                            unsigned, CUstream, void**, void**) = nullptr;
   CUresult (*GetErrorString)(CUresult, const char**) = nullptr;
   CUresult (*OccupancyMaxActiveClusters)(int*, CUfunction, const CUlaunchConfig*) = nullptr;
+  CUresult (*OccupancyMaxActiveBlocksPerMultiprocessor)(int*, CUfunction, int, size_t) = nullptr;
 };
 
 template <typename F>
@@ -81,6 +82,7 @@ Driver& driver() {
     ok = ok && load_entry("cuLaunchKernel", d.LaunchKernel, d.why);
     ok = ok && load_entry("cuGetErrorString", d.GetErrorString, d.why);
     ok = ok && load_entry("cuOccupancyMaxActiveClusters", d.OccupancyMaxActiveClusters, d.why);
+    ok = ok && load_entry("cuOccupancyMaxActiveBlocksPerMultiprocessor", d.OccupancyMaxActiveBlocksPerMultiprocessor, d.why);
     d.ok = ok;
   });
   return d;
@@ -687,9 +689,20 @@ int evtb_plan_create(const evtb_desc* desc, evtb_plan** out) {
                        : (d.kind == EVTB_SOFTMAX || d.kind == EVTB_LAYERNORM) ? 3 : 5;
     const int rpc = d.rows_per_cta > 0 ? d.rows_per_cta : 1;
     const long long blocks = (d.M + rpc - 1) / rpc;
-    const int per_sm = 2048 / d.threads > 0 ? 2048 / d.threads : 1;
+    // CTAs that are resident together (registers decide, not only the thread count); when the row
+    // blocks do not fit, every CTA gets the same number of them (3.46 blocks per CTA would make all
+    // wait for the quarter that has 4)
+    int per_sm = 0;
+    if (drv.OccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, p->fn, d.threads, static_cast<size_t>(d.smem_bytes)) != CUDA_SUCCESS ||
+        per_sm < 1)
+      per_sm = 2048 / d.threads > 0 ? 2048 / d.threads : 1;
     const long long cap = 1ll * p->sm_count * per_sm;
-    p->grid = static_cast<int>(blocks < cap ? blocks : cap);
+    if (blocks <= cap) {
+      p->grid = static_cast<int>(blocks);
+    } else {
+      const long long iters = (blocks + cap - 1) / cap;
+      p->grid = static_cast<int>((blocks + iters - 1) / iters);
+    }
   }
   *out = p;
   return EVTB_OK;

@@ -103,6 +103,59 @@ def convolution_backward_weight_channel_last(grad_output_channel_last, input_cha
     return gw.permute(0, 2, 3, 1).contiguous()
 
 
+def _pool_args(kernel_size, stride, padding):
+    k, s, p = list(kernel_size), list(stride), list(padding)
+    if len(set(k)) != 1 or len(set(s)) != 1 or len(set(p)) != 1:
+        raise NotImplementedError("max-pool kernels take square windows, equal strides and equal paddings")
+    return int(k[0]), int(s[0]), int(p[0])
+
+
+@torch.fx.wrap
+def max_pool2d_with_indices_channel_last(inputs_cl, kernel_size, stride, padding):
+    """The reference's leaf (pass_decomposition.py:109-118): (output, indices), both channels-last.  On
+    half-precision CUDA tensors this library's kernel runs and `indices` is a uint8 tensor holding the
+    place of the maximum inside its window (r * k + t) -- opaque to everything but the backward leaf;
+    elsewhere the library call with its int64 indices."""
+    if inputs_cl.is_cuda and inputs_cl.dtype in (torch.float16, torch.bfloat16) and inputs_cl.shape[-1] % 8 == 0:
+        k, s, p = _pool_args(kernel_size, stride, padding)
+        x = inputs_cl.contiguous()
+        N, H, W, C = x.shape
+        P, Q = (H + 2 * p - k) // s + 1, (W + 2 * p - k) // s + 1
+        y = torch.empty(N, P, Q, C, dtype=x.dtype, device=x.device)
+        code = torch.empty(N, P, Q, C, dtype=torch.uint8, device=x.device)
+        lib = runtime.load_library()
+        st = lib.evtb_maxpool_forward(x.data_ptr(), _DT[x.dtype], N, H, W, C, k, s, p, y.data_ptr(), code.data_ptr(),
+                                      torch.cuda.current_stream().cuda_stream)
+        runtime._check(lib, st, "evtb_maxpool_forward")
+        runtime.KERNELS_ENQUEUED += 1
+        return y, code
+    out, idx = torch.ops.aten.max_pool2d_with_indices(inputs_cl.permute(0, 3, 1, 2), kernel_size, stride, padding)
+    return out.permute(0, 2, 3, 1), idx.permute(0, 2, 3, 1)
+
+
+@torch.fx.wrap
+def max_pool2d_with_indices_backward_channel_last(grad_output_cl, x_cl, kernel_size, stride, padding, dilation, ceil_mode,
+                                                  indices_cl):
+    """The reference's leaf (pass_decomposition.py:120-132).  `indices_cl` is what the forward leaf
+    returned: uint8 window places (this library's kernel) or int64 flat indices (the library call)."""
+    if indices_cl.dtype == torch.uint8:
+        if list(dilation) != [1, 1] or ceil_mode:
+            raise NotImplementedError("max-pool kernels: dilation 1, floor mode")
+        k, s, p = _pool_args(kernel_size, stride, padding)
+        dy = grad_output_cl.contiguous()
+        N, H, W, C = x_cl.shape
+        dx = torch.empty(N, H, W, C, dtype=dy.dtype, device=dy.device)
+        lib = runtime.load_library()
+        st = lib.evtb_maxpool_backward(dy.data_ptr(), indices_cl.contiguous().data_ptr(), _DT[dy.dtype], N, H, W, C, k, s, p,
+                                       dx.data_ptr(), torch.cuda.current_stream().cuda_stream)
+        runtime._check(lib, st, "evtb_maxpool_backward")
+        runtime.KERNELS_ENQUEUED += 1
+        return dx
+    g = torch.ops.aten.max_pool2d_with_indices_backward(grad_output_cl.permute(0, 3, 1, 2), x_cl.permute(0, 3, 1, 2), kernel_size,
+                                                        stride, padding, dilation, ceil_mode, indices_cl.permute(0, 3, 1, 2))
+    return g.permute(0, 2, 3, 1)
+
+
 @torch.fx.wrap
 def batch_norm_stat(input, reduction_factor):
     """Per-channel E[x], E[x^2] in fp32 over N, H, W of a channels-last tensor (the half of

@@ -25,7 +25,7 @@ EXPORTED_SYMBOLS = [
     "evtb_plan_workspace_bytes", "evtb_plan_num_main_operands", "evtb_plan_grid",
     "evtb_plan_set_profile_buffer", "evtb_launch",
     "evtb_launch_ex", "evtb_colsum_workspace_bytes", "evtb_colsum", "evtb_colsum_accumulate", "evtb_colsum_static_max_cols",
-    "evtb_colsum_static", "evtb_bn_apply", "evtb_bn_backward_reduce", "evtb_bn_backward_apply", "evtb_sddmm", "evtb_csr_build_workspace_bytes", "evtb_csr_build",
+    "evtb_colsum_static", "evtb_bn_apply", "evtb_bn_backward_reduce", "evtb_bn_backward_apply", "evtb_maxpool_forward", "evtb_maxpool_backward", "evtb_sddmm", "evtb_csr_build_workspace_bytes", "evtb_csr_build",
 ]
 
 
@@ -108,6 +108,8 @@ def load_library() -> ctypes.CDLL:
     lib.evtb_bn_apply.argtypes = [vp, i32, i64, i64, vp, vp, vp, vp, ctypes.c_float, vp, i32, vp, vp, vp, vp]
     lib.evtb_bn_backward_reduce.argtypes = [vp, vp, vp, vp, i32, i64, i64, vp, vp, vp, vp, vp]
     lib.evtb_bn_backward_apply.argtypes = [vp, vp, i32, i64, i64, vp, vp, vp, vp, ctypes.c_float, vp, vp, vp, vp]
+    lib.evtb_maxpool_forward.argtypes = [vp, i32, i64, i64, i64, i64, i32, i32, i32, vp, vp, vp]
+    lib.evtb_maxpool_backward.argtypes = [vp, vp, i32, i64, i64, i64, i64, i32, i32, i32, vp, vp]
     _lib = lib
     return lib
 

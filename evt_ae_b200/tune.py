@@ -57,6 +57,14 @@ def candidates(op: _FusedMatmulBase) -> List[GemmTileConfig]:
                 for bn in (256, 128):
                     add(bn, 8, sk)
                 add(256, 8, sk, True)
+        # cuts that fill whole rounds of the grid: units = tiles x cuts just below 1, 2 or 3 times the
+        # number of CTAs (148) or CTA pairs (74) -- 16 pair tiles cut 9 ways are 144 units on 74 pairs
+        # (1.95 rounds), cut 8 ways 128 units (1.73 rounds, the second one three quarters full)
+        pair_tiles = ((op.M + 255) // 256) * ((op.N + base.bn - 1) // base.bn) * op.L
+        for rounds in (1, 2, 3):
+            for sk, pair in ((rounds * 148 // max(tiles, 1), False), (rounds * 74 // max(pair_tiles, 1), True)):
+                if 1 <= sk <= min(num_k // 8, 16):
+                    add(base.bn, 8, sk, pair)
     return out
 
 
@@ -253,6 +261,7 @@ def main(argv=None):
     ap = argparse.ArgumentParser()
     ap.add_argument("--workload", default="bert")
     ap.add_argument("--compile-only", action="store_true")
+    ap.add_argument("--only", default="", help="comma-separated node names of the workload (default: all)")
     ap.add_argument("--out", default=tuning.TABLE_PATH)
     ap.add_argument("--iters", type=int, default=20)
     ap.add_argument("--min-gain", type=float, default=0.96,
@@ -271,6 +280,8 @@ def main(argv=None):
         tune_bn_stats(a.out, a.iters, a.min_gain)
         return
     specs = workload_specs(a.workload)
+    if a.only:
+        specs = {k: v for k, v in specs.items() if k in a.only.split(",")}
     def as_meta(ts):
         return [torch.empty(t.shape, dtype=t.dtype, device="meta") if t.device.type != "meta" else t for t in ts]
     if a.compile_only:

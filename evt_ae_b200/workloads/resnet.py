@@ -15,9 +15,11 @@ What the reference's decomposition pass makes of it (pass_decomposition.py:66-18
                       -> the same fused forward (+ statistics) and weight-gradient kernels on a window
                          view of the zero-padded image: the 7 taps of a filter row times the channels
                          become the 64 "channels" the kernels move at a time (ops.StemWindow)
-  max-pool, average pool + classifier + loss
-                      -> library / eager calls; pooling is the leaf the reference uses
-                         (pass_decomposition.py:109-132)
+  max-pool            -> the reference's leaves (pass_decomposition.py:109-132) on this library's kernels
+                         (ops.max_pool2d_with_indices_channel_last: one byte per output element
+                         instead of an int64 index)
+  average pool + classifier + loss
+                      -> eager calls on [batch, 2048] tensors
 """
 from __future__ import annotations
 
@@ -300,8 +302,7 @@ class ResNetStep:
         y0, mean0, msq0 = self.stem_fprop(xv, wv)
         rf0 = 1.0 / (y0.shape[0] * y0.shape[1] * y0.shape[2])
         a0, m0, r0 = ops.bn_apply(y0, mean0, msq0, p["stem.bn.g"], p["stem.bn.b"], cfg.eps, relu=True)
-        pooled, pool_idx = aten.max_pool2d_with_indices(a0.permute(0, 3, 1, 2), [3, 3], [2, 2], [1, 1])
-        x = pooled.permute(0, 2, 3, 1).contiguous()
+        x, pool_idx = ops.max_pool2d_with_indices_channel_last(a0, [3, 3], [2, 2], [1, 1])
         saved = []
         for pre, entries, dgeo in self.plan:
             xin = x
@@ -350,8 +351,7 @@ class ResNetStep:
             g, g2 = d, d_id
         dx = g + g2
         # max-pool, ReLU, batch norm and weight gradient of the stem (no data gradient: images)
-        da0 = aten.max_pool2d_with_indices_backward(dx.permute(0, 3, 1, 2), a0.permute(0, 3, 1, 2), [3, 3], [2, 2], [1, 1],
-                                                    [1, 1], False, pool_idx).permute(0, 2, 3, 1)
+        da0 = ops.max_pool2d_with_indices_backward_channel_last(dx, a0, [3, 3], [2, 2], [1, 1], [1, 1], False, pool_idx)
         dz0, sums0 = ops.bn_backward_reduce(da0, y0, m0, r0, act=a0)
         dy0, dg0, db0 = ops.bn_backward_apply(dz0, y0, m0, r0, p["stem.bn.g"], sums0, rf0)
         grads["stem.bn.g"], grads["stem.bn.b"] = dg0, db0

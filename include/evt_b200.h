@@ -207,6 +207,19 @@ int evtb_bn_backward_apply(const void* grad, const void* y, int32_t dtype, int64
                            const float* mean, const float* rstd, const void* gamma, const float* sums,
                            float reduction_factor, void* dy, void* dgamma, void* dbeta, evtb_stream stream);
 
+/* Max-pooling of a channels-last activation x [N, H, W, C] (fp16 / bf16, contiguous, C % 8 == 0), square
+ * window `kernel` <= 15, `stride`, zero-free padding `padding` (padded positions never win), floor mode,
+ * dilation 1: the reference's leaves max_pool2d_with_indices_channel_last and
+ * max_pool2d_with_indices_backward_channel_last (python/gtl/compiler/passes/pass_decomposition.py:109-132).
+ * Instead of the library's int64 index per output element, `code` holds one byte per output element:
+ * r * kernel + t, the place of the maximum inside its window (first maximum in scan order, a NaN wins --
+ * the library's rule).  y and code have N x P x Q x C elements, P = (H + 2 padding - kernel) / stride + 1.
+ * Backward: dx[n, h, w, c] = sum of dy over the windows that cover (h, w) and chose it. */
+int evtb_maxpool_forward(const void* x, int32_t dtype, int64_t N, int64_t H, int64_t W, int64_t C, int32_t kernel,
+                         int32_t stride, int32_t padding, void* y, uint8_t* code, evtb_stream stream);
+int evtb_maxpool_backward(const void* dy, const uint8_t* code, int32_t dtype, int64_t N, int64_t H, int64_t W, int64_t C,
+                          int32_t kernel, int32_t stride, int32_t padding, void* dx, evtb_stream stream);
+
 /* SDDMM on a CSR pattern (int32 indices, fp32 features, F % 4 == 0):
  * out[p] = dot(U[i, :], V[col[p], :]) for every stored (i, col[p]).  Edge gradients of a GCN
  * layer; the reference has no SDDMM (its GCN backward is a second SpMM,
