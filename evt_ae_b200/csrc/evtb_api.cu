@@ -530,7 +530,7 @@ int evtb_plan_create(const evtb_desc* desc, evtb_plan** out) {
     p->splits = (num_k + p->kb_per_split - 1) / p->kb_per_split;   // no empty unit
     if (p->splits > 1) {
       // every CTA of a pair parks its own 128 x tile_n half: 2 * tiles half tiles
-      p->partial_bytes = sizeof(float) * static_cast<size_t>(2 * tiles) * p->splits * evtb::kBM * d.tile_n;
+      p->partial_bytes = sizeof(float) * static_cast<size_t>(2 * tiles) * evtb::kBM * d.tile_n;
       p->workspace = p->partial_bytes + sizeof(unsigned int) * static_cast<size_t>(2 * tiles);
     }
     p->main_operands = 2;
@@ -574,7 +574,7 @@ int evtb_plan_create(const evtb_desc* desc, evtb_plan** out) {
     p->grid = static_cast<int>(units < p->sm_count ? units : p->sm_count);
     p->main_operands = 2;
     if (p->splits > 1) {
-      p->partial_bytes = sizeof(float) * static_cast<size_t>(tiles) * p->splits * evtb::kBM * d.tile_n;
+      p->partial_bytes = sizeof(float) * static_cast<size_t>(tiles) * evtb::kBM * d.tile_n;
       p->workspace = p->partial_bytes + sizeof(unsigned int) * static_cast<size_t>(tiles);
     }
   } else if (d.kind == EVTB_CONV_WGRAD) {
@@ -631,7 +631,7 @@ int evtb_plan_create(const evtb_desc* desc, evtb_plan** out) {
     const long long units = tiles * p->splits;
     p->grid = static_cast<int>(units < p->sm_count ? units : p->sm_count);
     if (p->splits > 1) {
-      p->partial_bytes = sizeof(float) * static_cast<size_t>(tiles) * p->splits * evtb::kBM * d.tile_n;
+      p->partial_bytes = sizeof(float) * static_cast<size_t>(tiles) * evtb::kBM * d.tile_n;
       p->workspace = p->partial_bytes + sizeof(unsigned int) * static_cast<size_t>(tiles);
     }
   } else if (d.kind == EVTB_CONV_FPROP || d.kind == EVTB_CONV_DGRAD) {

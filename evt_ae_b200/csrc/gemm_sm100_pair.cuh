@@ -267,10 +267,10 @@ __device__ __forceinline__ void gemm_pair_kernel_body(const GemmParams& p) {
         if (lane == 0) mbar_arrive_cluster(leader_tmem_empty + static_cast<uint32_t>(as) * 8u);
         epi.tile_end(c);
       } else {
-        // 1. park this CTA's half of the unit's partial accumulator: [BN/4][128 rows] of float4
-        const int sp = u - t * p.splits;
+        // 1. add this CTA's half of the unit's partial accumulator to the half tile's fp32 sum in the
+        //    workspace ([BN/4][128 rows] of float4, 16-byte reductions at the L2; see gemm_sm100.cuh)
         const long long half = 2ll * t + rank;
-        float4* mine = reinterpret_cast<float4*>(p.partial + (half * p.splits + sp) * kBM * Cfg::BN) + quad * 32 + lane;
+        float4* mine = reinterpret_cast<float4*>(p.partial + half * kBM * Cfg::BN) + quad * 32 + lane;
 #pragma unroll 1
         for (int ch = col_group; got && ch < Cfg::BN / 32; ch += Cfg::COL_GROUPS) {
           float acc[32];
@@ -278,7 +278,7 @@ __device__ __forceinline__ void gemm_pair_kernel_body(const GemmParams& p) {
           float4* dst = mine + ch * 8 * kBM;
 #pragma unroll
           for (int q4 = 0; q4 < 8; ++q4)
-            __stcg(dst + q4 * kBM, make_float4(acc[4 * q4], acc[4 * q4 + 1], acc[4 * q4 + 2], acc[4 * q4 + 3]));
+            red_add_f32x4(dst + q4 * kBM, acc[4 * q4], acc[4 * q4 + 1], acc[4 * q4 + 2], acc[4 * q4 + 3]);
         }
         tcgen05_fence_before_sync();
         __syncwarp();
@@ -301,33 +301,18 @@ __device__ __forceinline__ void gemm_pair_kernel_body(const GemmParams& p) {
         if (hdr->is_last) {
           __threadfence();
           epi.tile_begin(c);
-          const float4* base = reinterpret_cast<const float4*>(p.partial + half * p.splits * kBM * Cfg::BN) + quad * 32 + lane;
+          float4* base = reinterpret_cast<float4*>(p.partial + half * kBM * Cfg::BN) + quad * 32 + lane;
 #pragma unroll 1
           for (int ch = col_group; ch < Cfg::BN / 32; ch += Cfg::COL_GROUPS) {
             float acc[32];
+            float4* src = base + ch * 8 * kBM;
+            float4 v[8];
 #pragma unroll
-            for (int j = 0; j < 32; ++j) acc[j] = 0.f;
-            // up to four partials x 16 columns in flight per thread; added in split order
-            for (int s2 = 0; s2 < p.splits; s2 += 4) {
+            for (int q4 = 0; q4 < 8; ++q4) v[q4] = __ldcg(src + q4 * kBM);
 #pragma unroll
-              for (int h = 0; h < 2; ++h) {
-                float4 v[4][4];
-#pragma unroll
-                for (int s3 = 0; s3 < 4; ++s3) {
-                  const float4* src = base + (static_cast<long long>(s2 + s3) * (Cfg::BN / 4) + ch * 8 + h * 4) * kBM;
-#pragma unroll
-                  for (int q4 = 0; q4 < 4; ++q4)
-                    v[s3][q4] = (s2 + s3 < p.splits) ? __ldcg(src + q4 * kBM) : make_float4(0.f, 0.f, 0.f, 0.f);
-                }
-#pragma unroll
-                for (int s3 = 0; s3 < 4; ++s3) {
-#pragma unroll
-                  for (int q4 = 0; q4 < 4; ++q4) {
-                    const int o = 16 * h + 4 * q4;
-                    acc[o] += v[s3][q4].x; acc[o + 1] += v[s3][q4].y; acc[o + 2] += v[s3][q4].z; acc[o + 3] += v[s3][q4].w;
-                  }
-                }
-              }
+            for (int q4 = 0; q4 < 8; ++q4) {
+              __stcg(src + q4 * kBM, make_float4(0.f, 0.f, 0.f, 0.f));     // ready for the next launch
+              acc[4 * q4] = v[q4].x; acc[4 * q4 + 1] = v[q4].y; acc[4 * q4 + 2] = v[q4].z; acc[4 * q4 + 3] = v[q4].w;
             }
             if (c.n0 + ch * 32 < p.N) epi.visit(c, c.n0 + ch * 32, acc);
           }

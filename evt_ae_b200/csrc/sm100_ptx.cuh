@@ -432,6 +432,11 @@ __device__ __forceinline__ void umma_commit_pair(uint64_t* bar, uint16_t cta_mas
 // ---------------------------------------------------------------------------
 // Global memory helpers
 // ---------------------------------------------------------------------------
+// four fp32 additions into global memory as one 16-byte reduction (performed at the L2)
+__device__ __forceinline__ void red_add_f32x4(float4* addr, float a, float b, float c, float d) {
+  asm volatile("red.global.add.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(addr), "f"(a), "f"(b), "f"(c), "f"(d) : "memory");
+}
+
 __device__ __forceinline__ void red_add_f32(float* addr, float v) {
   asm volatile("red.global.add.f32 [%0], %1;" ::"l"(addr), "f"(v) : "memory");
 }
