@@ -224,10 +224,22 @@ __device__ __forceinline__ float op_gelu_backward_tanh(float g, float x) {
   const float du = 0.7978845608028654f * (1.f + 0.134145f * x2);
   return g * (0.5f * (1.f + t) + 0.5f * x * (1.f - t * t) * du);
 }
+// d/dx [x Phi(x)] = Phi(x) + x phi(x).  The exponential of the Abramowitz & Stegun form of
+// erf(x / sqrt 2) is exp(-x^2 / 2), the same one the density needs: one exp2 and one reciprocal per
+// element (the special-function unit, 16 results per clock and SM, is what a GELU epilogue on a short-K
+// GEMM runs out of first).
 __device__ __forceinline__ float op_gelu_backward_erf(float g, float x) {
-  const float cdf = 0.5f * (1.f + fast_erf(x * 0.7071067811865476f));
-  const float pdf = __expf(-0.5f * x * x) * 0.3989422804014327f;
-  return g * (cdf + x * pdf);
+  const float ax = fabsf(x) * 0.7071067811865476f;
+  const float t = __fdividef(1.0f, fmaf(0.3275911f, ax, 1.0f));
+  float y = fmaf(t, 1.061405429f, -1.453152027f);
+  y = fmaf(t, y, 1.421413741f);
+  y = fmaf(t, y, -0.284496736f);
+  y = fmaf(t, y, 0.254829592f);
+  y *= t;
+  const float e = __expf(-0.5f * x * x);
+  const float erf_abs = fmaf(-y, e, 1.0f);
+  const float cdf = fmaf(0.5f, copysignf(erf_abs, x), 0.5f);
+  return g * fmaf(x * 0.3989422804014327f, e, cdf);
 }
 
 // ---------------------------------------------------------------------------
