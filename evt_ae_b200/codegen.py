@@ -98,7 +98,7 @@ class EpilogueSource:
 class EpilogueGenerator:
     def __init__(self, ir: EpilogueIR, struct_name: str = "Epi", row_tile: int = 128, col_group: int = 32,
                  staged: bool = False, max_stage_tiles: int = 8, tma_store: bool = False,
-                 defer_col_reductions: bool = False):
+                 defer_col_reductions: bool = False, double_buffer: bool = False):
         """row_tile: rows a CTA covers per step (a row predicate is needed unless M is a
         multiple of it; 0 = always predicate); col_group: columns the kernel guarantees to be
         in range whenever it calls visit8 with an in-range first column."""
@@ -117,6 +117,9 @@ class EpilogueGenerator:
         # [N]-vector reductions of a tensor-core kernel (32-column chunks, per-warp staging memory) may
         # collect a column strip's partial results before they go to global memory
         self.defer_col_reductions = defer_col_reductions and col_group == 32
+        # two sets of staging tiles used by alternate chunks: the pack of chunk i + 1 does not wait for
+        # the copy engine to finish reading chunk i's tiles
+        self.double_buffer = double_buffer
         self.deferred = 0
         self.finish: List[str] = []       # once per warp after its last tile
         self.uses_rand = False
@@ -274,7 +277,8 @@ class EpilogueGenerator:
                 self.pre_marks.append((mark[0], len(self.body_pre), mark[1], len(self.body_elem)))
                 if len(self.chunk_begin) != mark[2]:
                     self.pre_private = False
-        return EpilogueSource(self._assemble(), self.slots, self.uses_rand, self.stage_tiles, self.tma_stores)
+        code = self._assemble()
+        return EpilogueSource(code, self.slots, self.uses_rand, self.stage_tiles * (2 if self.double_buffer else 1), self.tma_stores)
 
     def _gen_node(self, node: Node, val: Dict[str, str]):
         ir = self.ir
@@ -403,10 +407,10 @@ class EpilogueGenerator:
                 "uint4 v = make_uint4(0u, 0u, 0u, 0u);",
                 f"const long long off = {off};",
                 f"if ({row_in} && {self._col_ok('nn')} && EVTB_CHK(c, off, 8, {t.numel}LL, {slot})) v = __ldg(reinterpret_cast<const uint4*>({base} + off * {eb}));",
-                f"stage_write16(c.stage + {r} * kStageTileBytes, row, seg, v);"])]
+                f"stage_write16(stg(c, {r}), row, seg, v);"])]
             self.chunk_begin.append("}")
             self.body_pre.append(f"float a_{nm}[8];")
-            self.body_pre.append(f"Pack8<{ct}>::unpack(stage_read16(c.stage + {r} * kStageTileBytes, c.lane, G), a_{nm});")
+            self.body_pre.append(f"Pack8<{ct}>::unpack(stage_read16(stg(c, {r}), c.lane, G), a_{nm});")
             return f"a_{nm}[j]"
         self.members.append(f"long long ro_{nm};")
         self.begin.append(f"ro_{nm} = {self._row_offset(t)};")
@@ -524,12 +528,12 @@ class EpilogueGenerator:
         if r is not None:
             self.body_pre.append(f"float o_{nm}[8];")
             self.body_elem.append(f"o_{nm}[j] = {val[node.args[0]]};")
-            self.body_post.append(f"stage_write16(c.stage + {r} * kStageTileBytes, c.lane, G, Pack8<{ct}>::pack(o_{nm}));")
+            self.body_post.append(f"stage_write16(stg(c, {r}), c.lane, G, Pack8<{ct}>::pack(o_{nm}));")
             lin = self._linear_strides(t) if (self.tma_store and len(self.tma_stores) < 4) else None
             if lin is not None:
                 j = len(self.tma_stores)
                 self.tma_stores.append(TmaStore(slot, lin[0], lin[1]))
-                self.tma_issue.append(f"tma_store_3d(&c.ep->tmap[{j}], c.stage + {r} * kStageTileBytes, n, c.m_warp, c.l);   // {nm}")
+                self.tma_issue.append(f"tma_store_3d(&c.ep->tmap[{j}], stg(c, {r}), n, c.m_warp, c.l);   // {nm}")
                 self.alias_wait = self.alias_wait or aliased
                 return
             row_in = "true" if self.rows_full else f"m < {self.ir.M}"
@@ -538,7 +542,7 @@ class EpilogueGenerator:
             self.chunk_stores += ["  " + x for x in self._stage_copy_loop([
                 f"const long long off = {off};",
                 f"if ({row_in} && {self._owner_pred(t, m='m', l='c.l')} && {self._col_ok('nn')} && EVTB_CHK(c, off, 8, {t.numel}LL, {slot}))",
-                f"  *reinterpret_cast<uint4*>({base} + off * {eb}) = stage_read16(c.stage + {r} * kStageTileBytes, row, seg);"])]
+                f"  *reinterpret_cast<uint4*>({base} + off * {eb}) = stage_read16(stg(c, {r}), row, seg);"])]
             self.chunk_stores.append("}")
             return
         self.members.append(f"long long ro_{nm};")
@@ -642,6 +646,14 @@ class EpilogueGenerator:
         s = []
         s.append(f"struct {self.struct_name} {{")
         s.append(ind(self.members, 2))
+        if self.double_buffer and self.stage_tiles:
+            sets = self.stage_tiles
+            s.append("  int dbuf_ = 0;   // which of the two sets of staging tiles this chunk uses")
+            s.append("  __device__ __forceinline__ char* stg(const EpiCtx& c, const int r) const {")
+            s.append(f"    return c.stage + (r + dbuf_ * {sets}) * kStageTileBytes;")
+            s.append("  }")
+        else:
+            s.append("  __device__ __forceinline__ char* stg(const EpiCtx& c, const int r) const { return c.stage + r * kStageTileBytes; }")
         s.append(ind(self.methods, 2))
         s.append("  __device__ __forceinline__ void tile_begin(const EpiCtx& c) {")
         s.append(ind(self.begin, 4))
@@ -686,7 +698,7 @@ class EpilogueGenerator:
         s.append("  __device__ __forceinline__ void chunk_begin(const EpiCtx& c, const int n) {")
         if self.alias_wait:
             s.append("    // a result tile doubles as an aux-load tile: the copy engine must have read it")
-            s.append("    if (c.lane == 0) tma_store_wait_read<0>();")
+            s.append(f"    if (c.lane == 0) tma_store_wait_read<{1 if self.double_buffer else 0}>();")
             s.append("    __syncwarp();")
         s.append(ind(self.chunk_begin, 4))
         if self.chunk_begin:
@@ -707,11 +719,17 @@ class EpilogueGenerator:
         if self.chunk_stores:
             s.append("    __syncwarp();   // tiles may be overwritten by the next chunk")
         s.append(ind(self.chunk_end, 4))
+        if self.double_buffer and self.stage_tiles:
+            s.append("    dbuf_ ^= 1;")
         s.append("  }")
         s.append("  __device__ __forceinline__ void body(const EpiCtx& c, const int n, const float (&acc)[32]) {")
         if self.tma_stores:
-            s.append("    // the copy engine must be done reading the staging tiles of the previous chunk")
-            s.append("    if (c.lane == 0) tma_store_wait_read<0>();")
+            if self.double_buffer:
+                s.append("    // the copy engine must be done reading this set of staging tiles (the chunk before the previous one)")
+                s.append("    if (c.lane == 0) tma_store_wait_read<1>();")
+            else:
+                s.append("    // the copy engine must be done reading the staging tiles of the previous chunk")
+                s.append("    if (c.lane == 0) tma_store_wait_read<0>();")
             s.append("    __syncwarp();")
         s.append("    visit8<0>(c, n, acc);")
         s.append("    visit8<1>(c, n + 8, acc + 8);")
@@ -753,6 +771,7 @@ class GemmTileConfig:
     tma_store: bool = True    # results with a linear address leave through TMA bulk stores
     staged: bool = True       # full tensors of the epilogue pass through shared-memory staging tiles
     row_resident: bool = False  # 128 x 512 tile = whole rows: a row-wise step runs in the epilogue (set by gemm_source)
+    double_buffer: bool = False  # two sets of staging tiles used by alternate chunks (TMA-store epilogues)
 
     @property
     def threads(self) -> int:
@@ -765,7 +784,8 @@ def gemm_source(ir: EpilogueIR, a_major: str, b_major: str, dtype: torch.dtype,
     description, entry-point name)."""
     # a CTA pair covers 256 rows per tile: rows 128..255 of the last tile are out of range unless
     # M is a multiple of 256
-    epi = EpilogueGenerator(ir, row_tile=256 if cfg.cta_pair else 128, staged=cfg.staged, tma_store=cfg.tma_store and cfg.staged).generate()
+    epi = EpilogueGenerator(ir, row_tile=256 if cfg.cta_pair else 128, staged=cfg.staged, tma_store=cfg.tma_store and cfg.staged,
+                            double_buffer=cfg.double_buffer and cfg.tma_store and cfg.staged).generate()
     cfg.stage_tiles = epi.stage_tiles
     # the staging tiles come out of the shared memory the operand ring would otherwise get
     while cfg.stages > 2 and gemm_smem_bytes(cfg) > 227 * 1024:
@@ -778,7 +798,8 @@ def gemm_source(ir: EpilogueIR, a_major: str, b_major: str, dtype: torch.dtype,
         cfg.row_resident, cfg.cta_pair, cfg.split_k, cfg.bn = True, False, 1, 512
         if cfg.epi_warps not in (8, 16):
             cfg.epi_warps = 16
-        epi = EpilogueGenerator(ir, row_tile=128, staged=True, tma_store=cfg.tma_store).generate()
+        epi = EpilogueGenerator(ir, row_tile=128, staged=True, tma_store=cfg.tma_store,
+                                double_buffer=cfg.double_buffer and cfg.tma_store).generate()
         cfg.stage_tiles = epi.stage_tiles
         cfg.stages = min(cfg.stages, 4)
         while cfg.stages > 2 and gemm_smem_bytes(cfg) > 227 * 1024:

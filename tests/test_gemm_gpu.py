@@ -96,3 +96,14 @@ def test_split_k_weight_gradient_twice(cuda_device):
         fused.check_status()
         st = compare(out, ref, "half")
         assert st["bad_frac"] == 0.0, st
+
+
+@pytest.mark.parametrize("pair", [False, True])
+def test_two_sets_of_staging_tiles(pair, cuda_device):
+    """GemmTileConfig.double_buffer: alternate 32-column chunks use alternate sets of staging tiles (the
+    TMA store of one chunk may still be reading its tiles while the next chunk is packed).  Same results;
+    measured on the BERT nodes it neither helps nor hurts, so it stays an option that is off by default."""
+    from evt_ae_b200.codegen import GemmTileConfig
+    for case in (P.mm_bias_gelu(512, 1024, 512, 128, 4, torch.bfloat16, "tanh"), P.mm_multi_store(512, 512, 256, 128, 4, torch.float16)):
+        fused = run_case(case, cuda_device, tile=GemmTileConfig(bn=128, stages=4, cta_pair=pair, double_buffer=True))
+        assert "dbuf_" in fused.source
