@@ -7,6 +7,7 @@
 #include <cuda_runtime.h>
 
 #include <cstdio>
+#include <cstdlib>
 #include <cstring>
 #include <fstream>
 #include <mutex>
@@ -42,6 +43,7 @@ struct Driver {
   CUresult (*FuncSetAttribute)(CUfunction, CUfunction_attribute, int) = nullptr;
   CUresult (*LaunchKernel)(CUfunction, unsigned, unsigned, unsigned, unsigned, unsigned, unsigned,
                            unsigned, CUstream, void**, void**) = nullptr;
+  CUresult (*LaunchKernelEx)(const CUlaunchConfig*, CUfunction, void**, void**) = nullptr;
   CUresult (*GetErrorString)(CUresult, const char**) = nullptr;
   CUresult (*OccupancyMaxActiveClusters)(int*, CUfunction, const CUlaunchConfig*) = nullptr;
   CUresult (*OccupancyMaxActiveBlocksPerMultiprocessor)(int*, CUfunction, int, size_t) = nullptr;
@@ -80,6 +82,7 @@ Driver& driver() {
     ok = ok && load_entry("cuModuleGetFunction", d.ModuleGetFunction, d.why);
     ok = ok && load_entry("cuFuncSetAttribute", d.FuncSetAttribute, d.why);
     ok = ok && load_entry("cuLaunchKernel", d.LaunchKernel, d.why);
+    ok = ok && load_entry("cuLaunchKernelEx", d.LaunchKernelEx, d.why);
     ok = ok && load_entry("cuGetErrorString", d.GetErrorString, d.why);
     ok = ok && load_entry("cuOccupancyMaxActiveClusters", d.OccupancyMaxActiveClusters, d.why);
     ok = ok && load_entry("cuOccupancyMaxActiveBlocksPerMultiprocessor", d.OccupancyMaxActiveBlocksPerMultiprocessor, d.why);
@@ -187,6 +190,39 @@ int encode_store_map(CUtensorMap* map, void* base, int64_t cols, int64_t rows, i
 int ceil_div(int a, int b) { return (a + b - 1) / b; }
 
 constexpr long long kIntMax = 0x7fffffffLL;
+
+// Programmatic dependent launch between consecutive tensor-core kernels of a stream (their set-up then
+// overlaps the predecessor's last tiles).  Off unless EVT_B200_PDL=1: measured on the BERT-large and
+// ResNet-50 steps (CUDA graphs of some 800 and 320 launches) it changed the step time by less than
+// 0.5 % either way, so the plain launch stays the default.
+bool pdl_enabled() {
+  static const bool on = [] {
+    const char* e = std::getenv("EVT_B200_PDL");
+    return e != nullptr && std::string(e) == "1";
+  }();
+  return on;
+}
+
+// One launch of a tensor-core kernel (the generated kernels call griddepcontrol.wait after their set-up).
+CUresult launch_tensor_kernel(CUfunction fn, int grid, int threads, int smem, CUstream stream, void** args) {
+  Driver& drv = driver();
+  if (!pdl_enabled()) return drv.LaunchKernel(fn, grid, 1, 1, threads, 1, 1, smem, stream, args, nullptr);
+  CUlaunchAttribute attr;
+  std::memset(&attr, 0, sizeof(attr));
+  attr.id = CU_LAUNCH_ATTRIBUTE_PROGRAMMATIC_STREAM_SERIALIZATION;
+  attr.value.programmaticStreamSerializationAllowed = 1;
+  CUlaunchConfig cfg;
+  std::memset(&cfg, 0, sizeof(cfg));
+  cfg.gridDimX = static_cast<unsigned>(grid);
+  cfg.gridDimY = cfg.gridDimZ = 1;
+  cfg.blockDimX = static_cast<unsigned>(threads);
+  cfg.blockDimY = cfg.blockDimZ = 1;
+  cfg.sharedMemBytes = static_cast<unsigned>(smem);
+  cfg.hStream = stream;
+  cfg.attrs = &attr;
+  cfg.numAttrs = 1;
+  return drv.LaunchKernelEx(&cfg, fn, args, nullptr);
+}
 
 // x as a strided view: all three strides or none, positive multiples of 8 elements
 const char* check_x_strides(const evtb_conv& g, bool allowed) {
@@ -806,8 +842,7 @@ int evtb_launch_ex(evtb_plan* plan, const void* const* ptrs, int n, void* worksp
       p.tile_counters = reinterpret_cast<unsigned int*>(static_cast<char*>(workspace) + plan->partial_bytes);
     }
     void* args[1] = {&p};
-    CUresult r = drv.LaunchKernel(plan->fn, plan->grid, 1, 1, d.threads, 1, 1, d.smem_bytes,
-                                  static_cast<CUstream>(stream), args, nullptr);
+    CUresult r = launch_tensor_kernel(plan->fn, plan->grid, d.threads, d.smem_bytes, static_cast<CUstream>(stream), args);
     if (r != CUDA_SUCCESS) return cu_fail("cuLaunchKernel(gemm)", r);
     return EVTB_OK;
   }
@@ -848,8 +883,7 @@ int evtb_launch_ex(evtb_plan* plan, const void* const* ptrs, int n, void* worksp
       p.tile_counters = reinterpret_cast<unsigned int*>(static_cast<char*>(workspace) + plan->partial_bytes);
     }
     void* args[1] = {&p};
-    CUresult r = drv.LaunchKernel(plan->fn, plan->grid, 1, 1, d.threads, 1, 1, d.smem_bytes,
-                                  static_cast<CUstream>(stream), args, nullptr);
+    CUresult r = launch_tensor_kernel(plan->fn, plan->grid, d.threads, d.smem_bytes, static_cast<CUstream>(stream), args);
     if (r != CUDA_SUCCESS) return cu_fail("cuLaunchKernel(convolution weight gradient)", r);
     return EVTB_OK;
   }
@@ -870,8 +904,7 @@ int evtb_launch_ex(evtb_plan* plan, const void* const* ptrs, int n, void* worksp
     cp.prof = nullptr;
     cp.epi = epi;
     void* cargs[1] = {&cp};
-    CUresult r = drv.LaunchKernel(plan->fn, plan->grid, 1, 1, d.threads, 1, 1, d.smem_bytes,
-                                  static_cast<CUstream>(stream), cargs, nullptr);
+    CUresult r = launch_tensor_kernel(plan->fn, plan->grid, d.threads, d.smem_bytes, static_cast<CUstream>(stream), cargs);
     if (r != CUDA_SUCCESS) return cu_fail("cuLaunchKernel(convolution)", r);
     return EVTB_OK;
   }
