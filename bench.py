@@ -1067,8 +1067,10 @@ def main():
                            f"({wl.bytes_exchanged_per_step / 1e6:.0f} MB of gathered operands per rank and step, NCCL), "
                            f"weight gradients all-reduced")
         else:
+            how = ("overlapped with the backward pass in four segments" if getattr(wl, "segments", None)
+                   else "after the step's single graph")
             parallelism = (f"dp{world}: one replica per GPU, per-GPU batch fixed, NCCL gradient all-reduce "
-                           f"({getattr(wl, 'bytes_reduced_per_step', 0) / 1e6:.0f} MB per step, overlapped with the backward pass in four segments)")
+                           f"({getattr(wl, 'bytes_reduced_per_step', 0) / 1e6:.0f} MB per step, {how})")
         line = dict(metric=wl.metric, value=value, unit=wl.unit, n_gpus=world, steps=args.steps,
                     warmup=args.warmup, ms_per_step=ms, higher_is_better=True, scaling=getattr(wl, "scaling", "weak"),
                     vs_baseline=None, dtype=wl.dtype, data="synthetic",
