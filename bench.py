@@ -431,24 +431,42 @@ class VitWorkload:
         torch.cuda.synchronize()
         self.step.check_status()
         before = runtime.KERNELS_ENQUEUED
-        self.graph = torch.cuda.CUDAGraph()
-        with torch.cuda.graph(self.graph, capture_error_mode="thread_local"):
-            self.s_loss, self.s_grads = whole()
+        self.graph = self.overlapped = self.segments = None
+        if dist.is_initialized() and dist.get_world_size() > 1:
+            # data parallel: the backward pass is cut after layers 9, 6 and 3; the gradients a stretch
+            # finished are all-reduced on a second stream while the next stretch computes
+            from evt_ae_b200.dp import OverlappedStep
+            cuts = {(3 * cfg.layers) // 4, cfg.layers // 2, cfg.layers // 4}
+
+            def parts():
+                tok, pm = self.step.embed_tokens(self.p, self.s_images)
+                for part in self.step.step_parts(self.p, tok, self.s_labels, cuts=cuts):
+                    if isinstance(part, tuple):
+                        loss, rest, dtok = part
+                        rest = dict(rest)
+                        rest.update(self.step.embed_backward(dtok, pm))
+                        yield loss, rest
+                    else:
+                        yield part
+            self.overlapped = OverlappedStep(parts)
+            self.segments = self.overlapped.segments
+            self.s_loss, self.s_grads = self.overlapped.final[0], self.overlapped.grads
+        else:
+            self.graph = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(self.graph, capture_error_mode="thread_local"):
+                self.s_loss, self.s_grads = whole()
         self.launches_per_step = runtime.KERNELS_ENQUEUED - before
         self.host_loss = torch.zeros((), dtype=torch.float32).pin_memory()
-        self.reducer = None
-        if dist.is_initialized() and dist.get_world_size() > 1:
-            from evt_ae_b200.dp import GradAllReducer
-            self.reducer = GradAllReducer(self.s_grads)
 
     @property
     def bytes_reduced_per_step(self):
-        return self.reducer.bytes_per_step if self.reducer is not None else 0
+        return self.overlapped.bytes_per_step if self.overlapped is not None else 0
 
     def _run(self):
-        self.graph.replay()
-        if self.reducer is not None:
-            self.reducer.allreduce(self.s_grads)
+        if self.overlapped is not None:
+            self.overlapped.replay()
+        else:
+            self.graph.replay()
         return self.s_loss
 
     def step_device(self):
@@ -559,24 +577,33 @@ class ResNetWorkload:
         torch.cuda.synchronize()
         self.step.check_status()
         before = runtime.KERNELS_ENQUEUED
-        self.graph = torch.cuda.CUDAGraph()
-        with torch.cuda.graph(self.graph, capture_error_mode="thread_local"):
-            self.s_loss, self.s_grads = self.step.step(self.p, self.s_images, self.s_labels)
+        self.graph = self.overlapped = self.segments = None
+        if dist.is_initialized() and dist.get_world_size() > 1:
+            # data parallel: the backward pass is cut after three quarters, half and a quarter of the
+            # bottleneck blocks; a stretch's gradients are all-reduced on a second stream while the next
+            # stretch computes
+            from evt_ae_b200.dp import OverlappedStep
+            nb = len(self.step.plan)
+            cuts = {(3 * nb) // 4, nb // 2, nb // 4}
+            self.overlapped = OverlappedStep(lambda: self.step.step_parts(self.p, self.s_images, self.s_labels, cuts=cuts))
+            self.segments = self.overlapped.segments
+            self.s_loss, self.s_grads = self.overlapped.final[0], self.overlapped.grads
+        else:
+            self.graph = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(self.graph, capture_error_mode="thread_local"):
+                self.s_loss, self.s_grads = self.step.step(self.p, self.s_images, self.s_labels)
         self.launches_per_step = runtime.KERNELS_ENQUEUED - before
         self.host_loss = torch.zeros((), dtype=torch.float32).pin_memory()
-        self.reducer = None
-        if dist.is_initialized() and dist.get_world_size() > 1:
-            from evt_ae_b200.dp import GradAllReducer
-            self.reducer = GradAllReducer(self.s_grads)
 
     @property
     def bytes_reduced_per_step(self):
-        return self.reducer.bytes_per_step if self.reducer is not None else 0
+        return self.overlapped.bytes_per_step if self.overlapped is not None else 0
 
     def _run(self):
-        self.graph.replay()
-        if self.reducer is not None:
-            self.reducer.allreduce(self.s_grads)
+        if self.overlapped is not None:
+            self.overlapped.replay()
+        else:
+            self.graph.replay()
         return self.s_loss
 
     def step_device(self):

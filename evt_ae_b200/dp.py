@@ -68,3 +68,54 @@ class GradAllReducer:
             if self.average:
                 flat.div_(self.world)
             torch._foreach_copy_(srcs, views)
+
+
+class OverlappedStep:
+    """A training step whose gradient exchange runs behind its backward pass.
+
+    `make_parts()` returns a generator over the step: it yields a dict of the parameter gradients that
+    became final since the last yield, any number of times, and last a tuple whose second element is the
+    dict of the remaining gradients (the workloads' `step_parts`).  Every stretch between two yields is
+    captured as its own CUDA graph (one memory pool, replayed in order); `replay()` replays them and,
+    after each, all-reduces that stretch's gradients on a second stream while the next graph runs.  Only
+    the last stretch's exchange is exposed.  `final` is the tuple the generator ended with."""
+
+    def __init__(self, make_parts, group=None):
+        pool = torch.cuda.graph_pool_handle()
+        gen = make_parts()
+        self.segments: List[list] = []      # [graph, gradients it finishes, their reducer]
+        self.final = None
+        while self.final is None:
+            g = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(g, pool=pool, capture_error_mode="thread_local"):
+                part = next(gen)
+            if isinstance(part, tuple):
+                self.final = part
+                part = part[1]
+            self.segments.append([g, dict(part), None])
+        gen.close()
+        self.comm = torch.cuda.Stream()
+        for seg in self.segments:
+            if seg[1]:
+                seg[2] = GradAllReducer(seg[1], group=group)
+
+    @property
+    def grads(self) -> Dict[str, torch.Tensor]:
+        out: Dict[str, torch.Tensor] = {}
+        for _, part, _ in self.segments:
+            out.update(part)
+        return out
+
+    @property
+    def bytes_per_step(self) -> int:
+        return sum(red.bytes_per_step for _, _, red in self.segments if red is not None)
+
+    def replay(self) -> None:
+        main = torch.cuda.current_stream()
+        for g, part, red in self.segments:
+            g.replay()
+            if red is not None:
+                self.comm.wait_stream(main)
+                with torch.cuda.stream(self.comm):
+                    red.allreduce(part)
+        main.wait_stream(self.comm)

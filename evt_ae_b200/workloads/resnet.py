@@ -286,16 +286,27 @@ class ResNetStep:
 
     # ---------------------------------------------------------------------------------- step
     def step(self, p: Dict[str, torch.Tensor], images: torch.Tensor, labels: torch.Tensor):
+        grads: Dict[str, torch.Tensor] = {}
+        for part in self.step_parts(p, images, labels):
+            if isinstance(part, tuple):
+                grads.update(part[1])
+                return part[0], grads
+            grads.update(part)
+
+    def step_parts(self, p: Dict[str, torch.Tensor], images: torch.Tensor, labels: torch.Tensor, cuts=()):
+        """The step as a generator, for overlapping a data-parallel gradient exchange with the backward
+        pass: yields the dict of parameter gradients finished since the last yield each time the backward
+        pass has completed a bottleneck block whose index (0 = first block of the network) is in `cuts`,
+        and at the end the tuple (loss, remaining gradients)."""
         cfg, dt = self.cfg, self.dtype
         F = torch.nn.functional
-        grads: Dict[str, torch.Tensor] = {}
         if self.arena is None or self.arena.buf.device != images.device:
             self.arena = ReductionArena(images.device, 1 << 19)
         self.arena.reset()
         with self.arena:
-            return self._step(p, images, labels, grads, cfg, dt, F)
+            yield from self._step(p, images, labels, {}, cfg, dt, F, set(cuts))
 
-    def _step(self, p, images, labels, grads, cfg, dt, F):
+    def _step(self, p, images, labels, grads, cfg, dt, F, cuts):
         # stem: the 7x7 / 2 convolution on 3 channels as a 7x1 convolution over 64-wide windows of the
         # zero-padded image (statistics in its epilogue), normalise + ReLU, library max-pool
         xv, wv = self.win.image(images, dt), self.win.filter(p["stem.w"])
@@ -333,7 +344,7 @@ class ResNetStep:
         g = (gfeat / hw_).to(dt).view(x.shape[0], 1, 1, x.shape[3]).expand_as(x).contiguous()
         g2 = None
         # ---------------------------------------------------------------- backward
-        for (pre, entries, dgeo), (xin, acts, dsave) in zip(reversed(self.plan), reversed(saved)):
+        for bi, (pre, entries, dgeo), (xin, acts, dsave) in zip(reversed(range(len(self.plan))), reversed(self.plan), reversed(saved)):
             # last convolution: the pass that takes the statistics also adds the two incoming
             # gradients and applies the mask of the ReLU after the residual addition
             name, geo = entries[2]
@@ -349,6 +360,9 @@ class ResNetStep:
             else:
                 d_id = dsum
             g, g2 = d, d_id
+            if bi in cuts and bi > 0:
+                done, grads = grads, {}
+                yield done
         dx = g + g2
         # max-pool, ReLU, batch norm and weight gradient of the stem (no data gradient: images)
         da0 = ops.max_pool2d_with_indices_backward_channel_last(dx, a0, [3, 3], [2, 2], [1, 1], [1, 1], False, pool_idx)
@@ -360,4 +374,4 @@ class ResNetStep:
         else:
             grads["stem.w"] = ops.convolution_backward_weight_channel_last(dy0, images.to(dt), p["stem.w"], [2, 2], [3, 3],
                                                                            [1, 1], False, [0, 0], 1)
-        return loss.detach(), grads
+        yield loss.detach(), grads

@@ -322,6 +322,20 @@ class VitStep:
         return loss.detach(), dict(zip(hp.keys(), grads[1:])), dx
 
     def step(self, p: Dict[str, torch.Tensor], tokens0: torch.Tensor, labels: torch.Tensor):
+        grads: Dict[str, torch.Tensor] = {}
+        for part in self.step_parts(p, tokens0, labels):
+            if isinstance(part, tuple):
+                loss, rest, dx = part
+                grads.update(rest)
+                return loss, grads, dx
+            grads.update(part)
+
+    def step_parts(self, p: Dict[str, torch.Tensor], tokens0: torch.Tensor, labels: torch.Tensor, cuts=()):
+        """The step as a generator, for overlapping a data-parallel gradient exchange with the backward
+        pass: yields the dict of parameter gradients finished since the last yield each time the backward
+        pass has completed a layer listed in `cuts`, and at the end the tuple (loss, remaining gradients,
+        dx of the tokens)."""
+        cuts = set(cuts)
         cfg, n, B = self.cfg, self.n, self.B
         S, D, nh = cfg.tokens_padded, cfg.dim, cfg.heads
         d = D // nh
@@ -383,4 +397,7 @@ class VitStep:
                 dn1, db_ln1, dg_ln1 = n.dgrad_d_res_ln(dv, p[pre + "v.w"], t2, xin, m1, r1)
                 grads[pre + "ln1.b"], grads[pre + "ln1.g"] = db_ln1, dg_ln1
                 dx = n.layernorm_bwd_add(dn1, xin, m1, r1, p[pre + "ln1.g"], p[pre + "ln1.b"], dxa)
-        return loss, grads, dx.view(S, B, D)
+                if i in cuts and i > 0:
+                    done, grads = grads, {}
+                    yield done
+            yield loss, grads, dx.view(S, B, D)
