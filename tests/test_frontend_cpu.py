@@ -17,7 +17,9 @@ import pytest
 import torch
 import torch.nn.functional as F
 
-REF = os.environ.get("EVT_REFERENCE_ROOT", "/root/reference")
+# a checkout of the reference: named by EVT_REFERENCE_ROOT, else a directory `reference` beside this repository
+REF = os.environ.get("EVT_REFERENCE_ROOT") or os.path.join(
+    os.path.dirname(os.path.dirname(os.path.dirname(os.path.abspath(__file__)))), "reference")
 pytestmark = pytest.mark.skipif(not os.path.isdir(os.path.join(REF, "python", "gtl", "compiler", "passes")),
                                 reason="no checkout of the reference here")
 
