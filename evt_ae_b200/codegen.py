@@ -934,7 +934,7 @@ def conv_source(ir: EpilogueIR, dgrad: bool, dtype: torch.dtype, cfg: ConvTileCo
         cfg.stages -= 1
     bf16 = "true" if dtype == torch.bfloat16 else "false"
     body = f"""// generated by evt_ae_b200.codegen -- do not edit
-{DEBUG_DEFINE()}#define EVTB_ROW_M(c, row) conv_row_to_m(*(c).conv, (c).conv_tile, (c).m_warp + (row))
+{DEBUG_DEFINE()}#define EVTB_ROW_M(c, row) ((c).m_rows[((row) >> 3) & 3])   /* row = i * 8 + lane / 4: mapped once per tile */
 #include "conv_sm100.cuh"
 #include "epilogue_ops.cuh"
 using namespace evtb;

@@ -283,6 +283,8 @@ __device__ __forceinline__ void conv_kernel_body(const ConvParams& p) {
       const uint32_t aph = (tile_iter >> 1) & 1;
       c.conv_tile = t;
       c.m_warp = quad * 32;                       // tile row of this warp's first row (see EVTB_ROW_M)
+#pragma unroll
+      for (int i = 0; i < 4; ++i) c.m_rows[i] = conv_row_to_m(p, t, quad * 32 + i * 8 + (lane >> 2));
       c.m = conv_row_to_m(p, t, quad * 32 + lane);
       c.n0 = t.n0;
       c.row_ok = c.m < p.M;

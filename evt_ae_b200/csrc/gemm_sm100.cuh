@@ -100,6 +100,8 @@ struct EpiCtx {
   int m_warp;   // first global row of this warp's 32 rows (convolutions: first tile row)
   const ConvParams* conv;   // convolution kernels only
   ConvTile conv_tile;
+  int m_rows[4];            // convolution kernels: canonical rows of the four tile rows (i * 8 + lane / 4) this
+                            // lane moves in the staged (coalesced) accesses, computed once per tile
 };
 
 // Canonical row of the `row`-th of this warp's 32 rows, for the staged (coalesced) accesses of
