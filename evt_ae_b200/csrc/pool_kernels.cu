@@ -29,37 +29,69 @@ struct PoolGeom {
   int N, H, W, C, P, Q, k, s, pad, kv;
 };
 
-// grid: x over Q * kv vectors of one output row, y = n * P + ph
-template <typename T>
+// Window size and stride as template arguments for the common cases (0 = read from the geometry): the
+// window loops unroll and the backward pass divides by a constant.  Index arithmetic avoids divisions by
+// run-time values (3-D grid: x over the vectors of one row, y = row, z = image; channel vectors per pixel
+// are split off with a shift when their count is a power of two): with them the backward pass executed
+// 430 instructions per 16-byte result and ran at 15 % of the HBM rate.
+template <int K, int S>
+struct PoolKS {
+  const int k, s;
+  __device__ __forceinline__ explicit PoolKS(const PoolGeom& g) : k(K ? K : g.k), s(S ? S : g.s) {}
+};
+
+__device__ __forceinline__ void pool_split(const PoolGeom& g, int i, int& pixel, int& cv) {
+  if ((g.kv & (g.kv - 1)) == 0) {
+    cv = i & (g.kv - 1);
+    pixel = i >> (31 - __clz(g.kv));
+  } else {
+    cv = i % g.kv;
+    pixel = i / g.kv;
+  }
+}
+
+// grid: x over Q * kv vectors of one output row, y = ph, z = n
+template <typename T, int K, int S>
 __global__ void __launch_bounds__(kPoolThreads)
 maxpool_forward_kernel(const T* __restrict__ x, T* __restrict__ y, uint8_t* __restrict__ code, PoolGeom g) {
+  const PoolKS<K, S> ks(g);
   const int i = blockIdx.x * kPoolThreads + threadIdx.x;
   if (i >= g.Q * g.kv) return;
-  const int cv = i % g.kv, pw = i / g.kv;
-  const int ph = blockIdx.y % g.P, n = blockIdx.y / g.P;
-  const int h0 = ph * g.s - g.pad, w0 = pw * g.s - g.pad;
+  int cv, pw;
+  pool_split(g, i, pw, cv);
+  const int ph = blockIdx.y, n = blockIdx.z;
+  const int h0 = ph * ks.s - g.pad, w0 = pw * ks.s - g.pad;
   float m[8];
   int best[8];
   const int r_first = h0 < 0 ? -h0 : 0, t_first = w0 < 0 ? -w0 : 0;
 #pragma unroll
   for (int j = 0; j < 8; ++j) {
     m[j] = -INFINITY;
-    best[j] = r_first * g.k + t_first;
+    best[j] = r_first * ks.k + t_first;
   }
-  for (int r = r_first; r < g.k && h0 + r < g.H; ++r) {
-    const T* row = x + ((static_cast<long long>(n) * g.H + (h0 + r)) * g.W) * g.C + cv * 8;
-    for (int t = t_first; t < g.k && w0 + t < g.W; ++t) {
+  const T* base = x + ((static_cast<long long>(n) * g.H) * g.W) * g.C + cv * 8;
+#pragma unroll
+  for (int r = 0; r < (K ? K : 15); ++r) {
+    if (r >= ks.k) break;
+    const int h = h0 + r;
+    if (h < 0 || h >= g.H) continue;
+    const T* row = base + static_cast<long long>(h) * g.W * g.C;
+#pragma unroll
+    for (int t = 0; t < (K ? K : 15); ++t) {
+      if (t >= ks.k) break;
+      const int w = w0 + t;
+      if (w < 0 || w >= g.W) continue;
       float v[8];
-      Vec8<T>::load(row + static_cast<long long>(w0 + t) * g.C, true, v);
+      Vec8<T>::load(row + static_cast<long long>(w) * g.C, true, v);
 #pragma unroll
       for (int j = 0; j < 8; ++j)
         if (v[j] > m[j] || v[j] != v[j]) {
           m[j] = v[j];
-          best[j] = r * g.k + t;
+          best[j] = r * ks.k + t;
         }
     }
   }
-  const long long o = ((static_cast<long long>(blockIdx.y) * g.Q + pw) * g.kv + cv) * 8;
+  const long long o = (((static_cast<long long>(n) * g.P + ph) * g.Q + pw) * g.kv + cv) * 8;
   Vec8<T>::store(y + o, true, m);
   uint2 packed;
   uint8_t* b = reinterpret_cast<uint8_t*>(&packed);
@@ -68,42 +100,50 @@ maxpool_forward_kernel(const T* __restrict__ x, T* __restrict__ y, uint8_t* __re
   *reinterpret_cast<uint2*>(code + o) = packed;
 }
 
-// grid: x over W * kv vectors of one input row, y = n * H + h
-template <typename T>
+// grid: x over W * kv vectors of one input row, y = h, z = n
+template <typename T, int K, int S>
 __global__ void __launch_bounds__(kPoolThreads)
 maxpool_backward_kernel(const T* __restrict__ dy, const uint8_t* __restrict__ code, T* __restrict__ dx, PoolGeom g) {
+  const PoolKS<K, S> ks(g);
   const int i = blockIdx.x * kPoolThreads + threadIdx.x;
   if (i >= g.W * g.kv) return;
-  const int cv = i % g.kv, w = i / g.kv;
-  const int h = blockIdx.y % g.H, n = blockIdx.y / g.H;
+  int cv, w;
+  pool_split(g, i, w, cv);
+  const int h = blockIdx.y, n = blockIdx.z;
   // windows ph with ph * s - pad <= h <= ph * s - pad + k - 1
   const int hp = h + g.pad, wp = w + g.pad;
-  int ph0 = hp - g.k + 1;
-  ph0 = ph0 > 0 ? (ph0 + g.s - 1) / g.s : 0;
-  int ph1 = hp / g.s;
+  int ph0 = hp - ks.k + 1;
+  ph0 = ph0 > 0 ? (ph0 + ks.s - 1) / ks.s : 0;
+  int ph1 = hp / ks.s;
   if (ph1 > g.P - 1) ph1 = g.P - 1;
-  int pw0 = wp - g.k + 1;
-  pw0 = pw0 > 0 ? (pw0 + g.s - 1) / g.s : 0;
-  int pw1 = wp / g.s;
+  int pw0 = wp - ks.k + 1;
+  pw0 = pw0 > 0 ? (pw0 + ks.s - 1) / ks.s : 0;
+  int pw1 = wp / ks.s;
   if (pw1 > g.Q - 1) pw1 = g.Q - 1;
   float acc[8];
 #pragma unroll
   for (int j = 0; j < 8; ++j) acc[j] = 0.f;
   for (int ph = ph0; ph <= ph1; ++ph) {
-    const int r = hp - ph * g.s;
+    const int r = hp - ph * ks.s;
     for (int pw = pw0; pw <= pw1; ++pw) {
-      const int mine = r * g.k + (wp - pw * g.s);
+      const int mine = r * ks.k + (wp - pw * ks.s);
       const long long o = (((static_cast<long long>(n) * g.P + ph) * g.Q + pw) * g.kv + cv) * 8;
       const uint2 packed = __ldg(reinterpret_cast<const uint2*>(code + o));
-      const uint8_t* b = reinterpret_cast<const uint8_t*>(&packed);
+      // the eight one-byte places against this position's place, four at a time (0xff per equal byte);
+      // most windows chose another position: their gradients are not even loaded
+      const unsigned want = static_cast<unsigned>(mine) * 0x01010101u;
+      const unsigned eq_lo = __vcmpeq4(packed.x, want), eq_hi = __vcmpeq4(packed.y, want);
+      if ((eq_lo | eq_hi) == 0u) continue;
       float v[8];
       Vec8<T>::load(dy + o, true, v);
 #pragma unroll
-      for (int j = 0; j < 8; ++j)
-        if (b[j] == mine) acc[j] += v[j];
+      for (int j = 0; j < 4; ++j) {
+        if ((eq_lo >> (8 * j)) & 1u) acc[j] += v[j];          // fp32 sums, as the library's kernel
+        if ((eq_hi >> (8 * j)) & 1u) acc[4 + j] += v[4 + j];
+      }
     }
   }
-  Vec8<T>::store(dx + ((static_cast<long long>(blockIdx.y) * g.W + w) * g.kv + cv) * 8, true, acc);
+  Vec8<T>::store(dx + (((static_cast<long long>(n) * g.H + h) * g.W + w) * g.kv + cv) * 8, true, acc);
 }
 
 static int pool_geom(const char* who, int32_t dtype, int64_t N, int64_t H, int64_t W, int64_t C, int32_t k, int32_t stride,
@@ -113,7 +153,7 @@ static int pool_geom(const char* who, int32_t dtype, int64_t N, int64_t H, int64
     return EVTB_EINVAL;
   }
   if (N <= 0 || H <= 0 || W <= 0 || C <= 0 || C % 8 != 0 || k < 1 || k > 15 || stride < 1 || pad < 0 || 2 * pad > k ||
-      N * H > 0x7fffffffLL || W * C > 0x7fffffffLL || N > 65535LL * 65535LL) {
+      W * C > 0x7fffffffLL || N > 65535 || H > 65535) {
     set_last_error(std::string(who) + ": needs C % 8 == 0, 1 <= kernel <= 15, stride >= 1, 0 <= 2 * padding <= kernel");
     return EVTB_EINVAL;
   }
@@ -141,14 +181,19 @@ int evtb_maxpool_forward(const void* x, int32_t dtype, int64_t N, int64_t H, int
     evtb::set_last_error("evtb_maxpool_forward: null pointer, or x / y not 16-byte (code not 8-byte) aligned");
     return EVTB_EINVAL;
   }
-  const long long rows = 1ll * g.N * g.P;
-  if (rows > 0x7fffffffLL) return EVTB_ETOOLARGE;
-  const dim3 grid((g.Q * g.kv + evtb::kPoolThreads - 1) / evtb::kPoolThreads, static_cast<unsigned>(rows));
+  if (g.P > 65535 || g.N > 65535) return EVTB_ETOOLARGE;
+  const dim3 grid((g.Q * g.kv + evtb::kPoolThreads - 1) / evtb::kPoolThreads, static_cast<unsigned>(g.P), static_cast<unsigned>(g.N));
   cudaStream_t s = static_cast<cudaStream_t>(stream);
-  if (dtype == EVTB_F16)
-    evtb::maxpool_forward_kernel<__half><<<grid, evtb::kPoolThreads, 0, s>>>(static_cast<const __half*>(x), static_cast<__half*>(y), code, g);
-  else
-    evtb::maxpool_forward_kernel<__nv_bfloat16><<<grid, evtb::kPoolThreads, 0, s>>>(static_cast<const __nv_bfloat16*>(x), static_cast<__nv_bfloat16*>(y), code, g);
+#define EVTB_POOL_FWD(T, K, S) evtb::maxpool_forward_kernel<T, K, S><<<grid, evtb::kPoolThreads, 0, s>>>( \
+      static_cast<const T*>(x), static_cast<T*>(y), code, g)
+#define EVTB_POOL_FWD_KS(T)                                   \
+  if (kernel == 3 && stride == 2) EVTB_POOL_FWD(T, 3, 2);     \
+  else if (kernel == 3 && stride == 1) EVTB_POOL_FWD(T, 3, 1); \
+  else if (kernel == 2 && stride == 2) EVTB_POOL_FWD(T, 2, 2); \
+  else EVTB_POOL_FWD(T, 0, 0)
+  if (dtype == EVTB_F16) { EVTB_POOL_FWD_KS(__half); } else { EVTB_POOL_FWD_KS(__nv_bfloat16); }
+#undef EVTB_POOL_FWD_KS
+#undef EVTB_POOL_FWD
   return cudaGetLastError() == cudaSuccess ? EVTB_OK : EVTB_ECUDA;
 }
 
@@ -161,14 +206,19 @@ int evtb_maxpool_backward(const void* dy, const uint8_t* code, int32_t dtype, in
     evtb::set_last_error("evtb_maxpool_backward: null pointer, or dy / dx not 16-byte (code not 8-byte) aligned");
     return EVTB_EINVAL;
   }
-  const long long rows = 1ll * g.N * g.H;
-  if (rows > 0x7fffffffLL) return EVTB_ETOOLARGE;
-  const dim3 grid((g.W * g.kv + evtb::kPoolThreads - 1) / evtb::kPoolThreads, static_cast<unsigned>(rows));
+  if (g.H > 65535 || g.N > 65535) return EVTB_ETOOLARGE;
+  const dim3 grid((g.W * g.kv + evtb::kPoolThreads - 1) / evtb::kPoolThreads, static_cast<unsigned>(g.H), static_cast<unsigned>(g.N));
   cudaStream_t s = static_cast<cudaStream_t>(stream);
-  if (dtype == EVTB_F16)
-    evtb::maxpool_backward_kernel<__half><<<grid, evtb::kPoolThreads, 0, s>>>(static_cast<const __half*>(dy), code, static_cast<__half*>(dx), g);
-  else
-    evtb::maxpool_backward_kernel<__nv_bfloat16><<<grid, evtb::kPoolThreads, 0, s>>>(static_cast<const __nv_bfloat16*>(dy), code, static_cast<__nv_bfloat16*>(dx), g);
+#define EVTB_POOL_BWD(T, K, S) evtb::maxpool_backward_kernel<T, K, S><<<grid, evtb::kPoolThreads, 0, s>>>( \
+      static_cast<const T*>(dy), code, static_cast<T*>(dx), g)
+#define EVTB_POOL_BWD_KS(T)                                   \
+  if (kernel == 3 && stride == 2) EVTB_POOL_BWD(T, 3, 2);     \
+  else if (kernel == 3 && stride == 1) EVTB_POOL_BWD(T, 3, 1); \
+  else if (kernel == 2 && stride == 2) EVTB_POOL_BWD(T, 2, 2); \
+  else EVTB_POOL_BWD(T, 0, 0)
+  if (dtype == EVTB_F16) { EVTB_POOL_BWD_KS(__half); } else { EVTB_POOL_BWD_KS(__nv_bfloat16); }
+#undef EVTB_POOL_BWD_KS
+#undef EVTB_POOL_BWD
   return cudaGetLastError() == cudaSuccess ? EVTB_OK : EVTB_ECUDA;
 }
 
