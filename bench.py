@@ -1043,8 +1043,8 @@ def main():
             is_ffn1 = isinstance(wl, BertLargeWorkload)
             roofline = dict(bound="tensor", achieved=achieved, peak=peak, unit="TFLOP/s", frac=achieved / peak,
                             traffic=FFN1_DRAM_TRAFFIC_BYTES if is_ffn1 else None,
-                            traffic_unit="bytes per launch (dram read + write), from the ncu capture summarised in "
-                                         "profiles/bert_ffn1_gemm_ncu_metrics.md, not measured in this run",
+                            traffic_unit=("bytes per launch (dram read + write), from the ncu capture summarised in "
+                                          "profiles/bert_ffn1_gemm_ncu_metrics.md, not measured in this run") if is_ffn1 else None,
                             algorithmic_bytes=FFN1_ALGORITHMIC_BYTES if is_ffn1 else None, kernel=kname, kernel_ms=kernel_ms,
                             peak_source=f"{peaks['source']} (burst: kernel timed alone)",
                             step_gemm_tflops=step_tflops, step_gemm_flops=wl.flops,
