@@ -109,3 +109,23 @@ def test_every_node_kind_has_candidates_and_a_table_entry_is_applied(tmp_path, m
             else:
                 assert int(getattr(cfg, f)) == v, (case.name, f)
     monkeypatch.setattr(tuning, "_table", None)
+
+
+def test_ffn1_profile_note_describes_the_kernel_the_benchmark_times():
+    """bench.py reports the FFN1 GEMM's DRAM traffic from a profiler capture summarised under profiles/;
+    the figure is only valid for the tile the capture ran with.  The note names that tile and the traffic:
+    both must agree with what the code uses now."""
+    import os
+    import re
+    import torch
+    from evt_ae_b200.workloads import bert as wb
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    note = open(os.path.join(root, "profiles", "bert_ffn1_gemm_ncu_metrics.md")).read()
+    m = re.search(r"(\d+) x (\d+)\s+pair tiles, (\d+)-stage ring, (\d+) epilogue warps", note)
+    assert m, "the note no longer names the tile"
+    step = wb.BertStep(wb.BERT_LARGE, 32, 512, dtype=torch.bfloat16)
+    tile = step.n.ops["lin_hf_gelu"].tile
+    assert tile.cta_pair and (256, tile.bn, tile.stages, tile.epi_warps) == tuple(int(v) for v in m.groups())
+    traffic = float(re.search(r"-> traffic ([0-9.]+) MB per launch", note).group(1)) * 1e6
+    src = open(os.path.join(root, "bench.py")).read()
+    assert abs(float(re.search(r"FFN1_DRAM_TRAFFIC_BYTES = ([0-9.e]+)", src).group(1)) - traffic) < 1e5
