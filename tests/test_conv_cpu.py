@@ -41,3 +41,30 @@ def test_stem_window_restates_the_convolution():
         ops.StemWindow((1, 8, 8, 4), (8, 3, 3, 4), [1, 1], [1, 1])       # stride 1 x 4 channels: 8-byte window steps
     with pytest.raises(NotImplementedError):
         ops.StemWindow((1, 64, 64, 16), (8, 7, 7, 16), [2, 2], [3, 3])   # 7 taps do not fit 4 pixels of 16 channels
+
+
+def test_generated_epilogue_options():
+    """What the code generator emits for the options that change an epilogue's structure (source level; the
+    GPU tests run the kernels): column sums of a convolution are held back across a column strip for tiles
+    of up to 128 columns and sent at once otherwise; the staged rows of a convolution take their output
+    positions from the per-tile table; a second set of staging tiles alternates per chunk."""
+    import torch
+    import partitions as P
+    from evt_ae_b200.codegen import ConvTileConfig, GemmTileConfig
+    from evt_ae_b200.fuser import fuse_module
+    case = P.conv_fprop_bn_stat(4, 28, 28, 128, 256, 3, 1)
+    metas = [torch.empty(x.shape, dtype=x.dtype, device="meta") for x in case.inputs]
+    _, narrow = fuse_module(case.module, metas, conv_tile=ConvTileConfig(bn=128))
+    _, wide = fuse_module(case.module, metas, conv_tile=ConvTileConfig(bn=256))
+    assert "flush_" in narrow.source and "dr_mask_" in narrow.source
+    assert "flush_" not in wide.source and "red_add_f32(" in wide.source
+    assert narrow.tile.stage_tiles == wide.tile.stage_tiles + 1          # the strip's partial sums
+    for op in (narrow, wide):
+        assert "(c).m_rows[" in op.source and "conv_row_to_m(*(c).conv" not in op.source
+    g = P.mm_bias_gelu(512, 1024, 512, 128, 4, torch.bfloat16, "tanh")
+    metas = [torch.empty(x.shape, dtype=x.dtype, device="meta") for x in g.inputs]
+    _, one = fuse_module(g.module, metas, tile=GemmTileConfig(bn=128, stages=4))
+    _, two = fuse_module(g.module, metas, tile=GemmTileConfig(bn=128, stages=4, double_buffer=True))
+    assert "dbuf_" not in one.source and "tma_store_wait_read<0>" in one.source
+    assert "dbuf_ ^= 1" in two.source and "tma_store_wait_read<1>" in two.source
+    assert two.tile.stage_tiles == 2 * one.tile.stage_tiles
