@@ -161,9 +161,6 @@ __device__ __forceinline__ void conv_kernel_body(const ConvParams& p) {
   tcgen05_fence_after_sync();
   const uint32_t tmem_base = hdr->tmem_base;
   const bool tmem_ok = tmem_addr_valid(tmem_base, Cfg::TMEM_COLS);   // same value in every thread
-  // set-up is done, nothing of global memory has been touched (see gemm_sm100.cuh)
-  griddep_launch_dependents();
-  griddep_wait();
 
   if (!tmem_ok) {
     if (threadIdx.x == 0) report_status(p.status, DEV_TMEM_ALLOC);

@@ -43,7 +43,6 @@ struct Driver {
   CUresult (*FuncSetAttribute)(CUfunction, CUfunction_attribute, int) = nullptr;
   CUresult (*LaunchKernel)(CUfunction, unsigned, unsigned, unsigned, unsigned, unsigned, unsigned,
                            unsigned, CUstream, void**, void**) = nullptr;
-  CUresult (*LaunchKernelEx)(const CUlaunchConfig*, CUfunction, void**, void**) = nullptr;
   CUresult (*GetErrorString)(CUresult, const char**) = nullptr;
   CUresult (*OccupancyMaxActiveClusters)(int*, CUfunction, const CUlaunchConfig*) = nullptr;
   CUresult (*OccupancyMaxActiveBlocksPerMultiprocessor)(int*, CUfunction, int, size_t) = nullptr;
@@ -82,7 +81,6 @@ Driver& driver() {
     ok = ok && load_entry("cuModuleGetFunction", d.ModuleGetFunction, d.why);
     ok = ok && load_entry("cuFuncSetAttribute", d.FuncSetAttribute, d.why);
     ok = ok && load_entry("cuLaunchKernel", d.LaunchKernel, d.why);
-    ok = ok && load_entry("cuLaunchKernelEx", d.LaunchKernelEx, d.why);
     ok = ok && load_entry("cuGetErrorString", d.GetErrorString, d.why);
     ok = ok && load_entry("cuOccupancyMaxActiveClusters", d.OccupancyMaxActiveClusters, d.why);
     ok = ok && load_entry("cuOccupancyMaxActiveBlocksPerMultiprocessor", d.OccupancyMaxActiveBlocksPerMultiprocessor, d.why);
@@ -191,37 +189,12 @@ int ceil_div(int a, int b) { return (a + b - 1) / b; }
 
 constexpr long long kIntMax = 0x7fffffffLL;
 
-// Programmatic dependent launch between consecutive tensor-core kernels of a stream (their set-up then
-// overlaps the predecessor's last tiles).  Off unless EVT_B200_PDL=1: measured on the BERT-large and
-// ResNet-50 steps (CUDA graphs of some 800 and 320 launches) it changed the step time by less than
-// 0.5 % either way, so the plain launch stays the default.
-bool pdl_enabled() {
-  static const bool on = [] {
-    const char* e = std::getenv("EVT_B200_PDL");
-    return e != nullptr && std::string(e) == "1";
-  }();
-  return on;
-}
-
-// One launch of a tensor-core kernel (the generated kernels call griddepcontrol.wait after their set-up).
+// One launch of a tensor-core kernel.  (Programmatic dependent launch between consecutive kernels was
+// tried here -- griddepcontrol.launch_dependents / wait after the kernels' set-up, launches with
+// programmatic stream serialisation -- and taken out again: the BERT-large and ResNet-50 steps changed by
+// less than 0.5 % either way; the sum of the kernels' own times is the step time.)
 CUresult launch_tensor_kernel(CUfunction fn, int grid, int threads, int smem, CUstream stream, void** args) {
-  Driver& drv = driver();
-  if (!pdl_enabled()) return drv.LaunchKernel(fn, grid, 1, 1, threads, 1, 1, smem, stream, args, nullptr);
-  CUlaunchAttribute attr;
-  std::memset(&attr, 0, sizeof(attr));
-  attr.id = CU_LAUNCH_ATTRIBUTE_PROGRAMMATIC_STREAM_SERIALIZATION;
-  attr.value.programmaticStreamSerializationAllowed = 1;
-  CUlaunchConfig cfg;
-  std::memset(&cfg, 0, sizeof(cfg));
-  cfg.gridDimX = static_cast<unsigned>(grid);
-  cfg.gridDimY = cfg.gridDimZ = 1;
-  cfg.blockDimX = static_cast<unsigned>(threads);
-  cfg.blockDimY = cfg.blockDimZ = 1;
-  cfg.sharedMemBytes = static_cast<unsigned>(smem);
-  cfg.hStream = stream;
-  cfg.attrs = &attr;
-  cfg.numAttrs = 1;
-  return drv.LaunchKernelEx(&cfg, fn, args, nullptr);
+  return driver().LaunchKernel(fn, grid, 1, 1, threads, 1, 1, smem, stream, args, nullptr);
 }
 
 // x as a strided view: all three strides or none, positive multiples of 8 elements

@@ -336,10 +336,6 @@ __device__ __forceinline__ void gemm_kernel_body(const GemmParams& p) {
   tcgen05_fence_after_sync();
   const uint32_t tmem_base = hdr->tmem_base;
   const bool tmem_ok = tmem_addr_valid(tmem_base, Cfg::TMEM_COLS);   // same value in every thread
-  // Set-up (barriers, tensor memory) is done and nothing of global memory has been touched: from here
-  // the next kernel's CTAs may move in behind this grid's, and this grid waits for its predecessor.
-  griddep_launch_dependents();
-  griddep_wait();
 
   if (!tmem_ok) {
     if (threadIdx.x == 0) report_status(p.status, DEV_TMEM_ALLOC);

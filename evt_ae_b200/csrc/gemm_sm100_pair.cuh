@@ -106,10 +106,6 @@ __device__ __forceinline__ void gemm_pair_kernel_body(const GemmParams& p) {
   tcgen05_fence_after_sync();
   const uint32_t tmem_base = hdr->tmem_base;
   const bool tmem_ok = tmem_addr_valid(tmem_base, Cfg::TMEM_COLS);   // same value in every thread
-  // Set-up (barriers, tensor memory) is done and nothing of global memory has been touched: from here
-  // the next kernel's CTAs may move in behind this grid's, and this grid waits for its predecessor.
-  griddep_launch_dependents();
-  griddep_wait();
 
   if (!tmem_ok) {
     // the peer's bounded waits run out and it meets this CTA at the cluster barrier below

@@ -432,13 +432,6 @@ __device__ __forceinline__ void umma_commit_pair(uint64_t* bar, uint16_t cta_mas
 // ---------------------------------------------------------------------------
 // Global memory helpers
 // ---------------------------------------------------------------------------
-// Programmatic dependent launch.  `launch_dependents`: the next kernel in the stream, if it was launched
-// with programmatic stream serialisation, may start taking SMs once every CTA of this grid has executed
-// this (or left).  `wait`: blocks until the grids this one depends on have completed and their memory
-// is visible.  Both do nothing in a launch without that attribute.
-__device__ __forceinline__ void griddep_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
-__device__ __forceinline__ void griddep_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
-
 // four fp32 additions into global memory as one 16-byte reduction (performed at the L2)
 __device__ __forceinline__ void red_add_f32x4(float4* addr, float a, float b, float c, float d) {
   asm volatile("red.global.add.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(addr), "f"(a), "f"(b), "f"(c), "f"(d) : "memory");
